@@ -364,6 +364,87 @@ int b200q_scatter_scaled_rows(const void* src_dev, const int32_t* pair_pos_dev, 
                               void* dst_dev, int T, int W, int dtype, void* stream);
 /* gated unit: gate_up row = [g (F) | u (F)]; y = silu(g) * u */
 int b200q_silu_glu(const void* gate_up_dev, void* y_dev, int64_t rows, int F, int dtype, void* stream);
+/* ---- pre-norm layers, token shift, and mixers 6-8 (prenorm_ops.cu, decay_attn.cu, window_attn.cu) -------------------------
+ * seq_desc / row_seq / state conventions as above. */
+
+/* plain RMS norm of fp32 rows, optionally followed by a token shift:
+ *   n[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w;   y[t] = n[t] + (n[t-1] - n[t]) * shift       (shift NULL: y = n)
+ * n[t-1] of a portion's first token is read from the sequence's state slot (zeros at position 0); the n of every
+ * sequence's last token is left in carry [n_seqs, W] (b200q_store_carry moves it into the slot once every reader
+ * of the old value has run).  rows != NULL (only without shift) gathers x[rows[i]] into output row i.
+ * y_t (model dtype) and / or y_f32 receive the result. */
+int b200q_rmsnorm_shift(const float* x_dev, const int32_t* rows_dev, const float* w_dev, const float* shift_dev,
+                        const float* state_dev, long long slot_stride, const int32_t* seq_desc_dev,
+                        const int32_t* row_seq_dev, int n_seqs, float* carry_dev, void* y_t_dev, float* y_f32_dev,
+                        int n, int W, float eps, int dtype, void* stream);
+/* state[slot of sequence s][0..W) <- src row of s: last_rows = 1: the last row of the sequence's portion in a
+ * [T, W] buffer; 0: row s of a [n_seqs, W] buffer */
+int b200q_store_carry(const float* src_dev, int last_rows, float* state_dev, long long slot_stride,
+                      const int32_t* seq_desc_dev, int n_seqs, int W, void* stream);
+/* n_mix blends of every row with the previous token's row: out[t, s*W + c] = h[t,c] + (h[t-1,c] - h[t,c]) *
+ * mu[s*W + c]; h fp32 [T, W]; h[t-1] of a portion's first token from the state slot (zeros at position 0);
+ * out [T, n_mix*W] in the model dtype */
+int b200q_shift_blend(const float* h_dev, const float* mu_dev, int n_mix, const float* state_dev,
+                      long long slot_stride, const int32_t* seq_desc_dev, const int32_t* row_seq_dev, void* out_dev,
+                      int T, int W, int dtype, void* stream);
+/* z <- relu(z)^2 in place over n values */
+int b200q_relu2(void* z_dev, int64_t n, int dtype, void* stream);
+/* out = tanh(in) (fp32 in, model dtype out) */
+int b200q_tanh_cast(const float* in_dev, void* out_dev, int64_t n, int dtype, void* stream);
+/* out[t, 0..C) = act(in[t, 0..C)) into fp32 rows; act 0 = none, 1 = SiLU */
+int b200q_act_to_f32(const void* in_dev, int ld_in, float* out_dev, int ld_out, int C, int act, int T, int dtype,
+                     void* stream);
+/* w <- exp(-exp(w + w0)) in place over fp32 rows of C values (row stride ldw; the fp32 model evaluates it
+ * through fp64) */
+int b200q_decay_from_logits(float* w_dev, int ldw, const float* w0_dev, int C, int T, int dtype, void* stream);
+/* linear attention with decay over the sequences of a step.  qkv: fp32 rows (ldq) holding q at q_off (heads*dim), k at
+ * k_off (heads*dim), v at v_off (heads*vdim).  state: fp32 [heads][dim][vdim] per slot.
+ *   head_decay != NULL (fp32 [heads]):    S <- decay_h S + k v^T;  o = S^T q
+ *   w != NULL (fp32 rows ldw, [heads*dim]), bonus fp32 [heads*dim]:   o = (S + diag(bonus) k v^T)^T q;  S <- diag(w) S + k v^T
+ * raw: fp32 [T, heads*vdim] */
+int b200q_decay_attn(const float* qkv_dev, int ldq, int q_off, int k_off, int v_off, const float* head_decay_dev,
+                     const float* w_dev, int ldw, const float* bonus_dev, float* state_dev, long long slot_stride,
+                     const int32_t* seq_desc_dev, int n_seqs, int heads, int dim, int vdim, float* raw_dev,
+                     void* stream);
+/* out[t, c] = raw[t, c] / sqrt(mean over c's group of raw^2 + eps) * w[c] * act(gate[t, c]); groups are `group`
+ * consecutive values of the C in a row; gate: model dtype rows (ld_gate); gate_act 0 = sigmoid, 1 = SiLU */
+int b200q_gated_rmsnorm(const float* raw_dev, int C, int group, const float* w_dev, const void* gate_dev,
+                        int ld_gate, int gate_act, float eps, void* out_dev, int T, int dtype, void* stream);
+/* window attention 1/2: proj row = [q (heads*dim) | k (kv_heads*dim) | v (kv_heads*vdim) | ...].  The first rot_dims
+ * dimensions of every q and k head are turned, dimension i with i + rot_dims/2, by position * freq[i] (freq: fp64
+ * [rot_dims/2]; rot_dims 0: none).  qs[t,h,:] = turned q * scale * temp[h] (fp32; temp NULL = 1); cache row
+ * slot_mapping[t] = [turned k | v] in the model dtype ([kv_heads*dim + kv_heads*vdim]) */
+int b200q_window_attn_prep(const void* proj_dev, int ldp, int heads, int kv_heads, int dim, int vdim, int rot_dims,
+                           const double* freq_dev, const int32_t* positions_dev, const int32_t* slot_mapping_dev,
+                           const float* temp_dev, float scale, float* qs_dev, void* cache_dev, int T, int dtype,
+                           void* stream);
+/* window attention 2/2: for token t at position p over keys max(0, p - window + 1) <= j <= p (window 0: all):
+ * out[t,h,:] = softmax_j(qs[t,h] . k_j) . v_j * sigmoid(gate[t,h]) (gate: model dtype rows with one value per
+ * head, stride ld_gate; NULL: no gate).  bf16 caches with dim, vdim in {64, 128} run on the tensor cores. */
+int b200q_window_attn(const float* qs_dev, const void* cache_dev, const int32_t* block_table_dev, int bt_stride,
+                      const int32_t* row_seq_dev, const int32_t* positions_dev, const int32_t* seq_desc_dev,
+                      int n_seqs, int T, int heads, int kv_heads, int dim, int vdim, int block_size, int window,
+                      const void* gate_dev, int ld_gate, void* out_dev, int dtype, void* stream);
+/* routing of the grouped mixture over fp32 router logits [T, E]: s = softmax(logits); choice = s + correction;
+ * only experts of the keep best of n_groups equal groups (group score = largest choice in it) may be chosen;
+ * the top largest choices (ties: lowest index) -> idx; wts = s of the chosen / (their sum + 1e-20).  Grouping
+ * outputs as in b200q_moe_route over E groups; the tile table lists the first e_gemm experts only (the rest are
+ * identity experts that run no product). */
+int b200q_moe_route_grouped(const float* logits_dev, const float* correction_dev, int T, int E, int e_gemm, int top,
+                            int n_groups, int keep, int32_t* idx_dev, float* wts_dev, int32_t* group_off_dev,
+                            int32_t* perm_tok_dev, int32_t* pair_pos_dev, int32_t* tile_tab_dev,
+                            int32_t* n_tiles_dev, void* stream);
+/* x += a_scale * a (+ b_scale * b, b may be NULL); a, b in the model dtype */
+int b200q_residual_add(float* x_dev, const void* a_dev, float a_scale, const void* b_dev, float b_scale, int T, int W,
+                       int dtype, void* stream);
+/* x[t] += sum_k wts[t,k] * (idx[t,k] < n_real ? expert_out[pair_pos[t*top+k]] : h[t]) */
+int b200q_residual_add_routed(float* x_dev, const void* expert_out_dev, const int32_t* pair_pos_dev,
+                              const int32_t* idx_dev, const float* wts_dev, int top, int n_real, const void* h_dev,
+                              int T, int W, int dtype, void* stream);
+/* out[t] = [a[t] | b[t]] (fp32 rows of W each) in the model dtype, [T, 2W] */
+int b200q_concat_cast(const float* a_dev, const float* b_dev, void* out_dev, int T, int W, int dtype, void* stream);
+/* l <- cap * tanh(l / cap) in place over n fp32 values */
+int b200q_softcap_f32(float* logits_dev, int64_t n, float cap, void* stream);
 int b200q_argmax_f32(const float* logits_dev, int32_t* ids_dev, int B, int V, void* stream);
 int b200q_f32_to_bf16(const float* in_dev, void* out_dev, int64_t n, void* stream);
 int b200q_copy_f32(const float* in_dev, float* out_dev, int64_t n, void* stream);
@@ -408,6 +489,9 @@ typedef struct b200q_model_config {
   int32_t input_taps;     /* post-norm form: every sublayer reads h + conv(h), a per-channel causal
                              convolution over time with this many taps ("canon1" / "canon2"); 0 = reads x    */
   int32_t learned_pos;    /* 1: a learned position table "pos" [>= max_pos, W] is added to the embedding     */
+  int32_t token_shift;    /* pre-norm form, 1: the mixer reads h + (h_prev - h) * shift ("shift" [1, W] per layer),
+                             h_prev = the previous token's normed row (zeros before the first token)           */
+  float logit_softcap;    /* layered architectures: logits <- cap * tanh(logits / cap); 0 = off                */
 } b200q_model_config;
 
 #define B200Q_ARCH_LLAMA 0
@@ -420,9 +504,16 @@ typedef struct b200q_model_config {
  * with grouped RMS norms, per-channel layer scales ls and causal input convolutions whose last inputs are
  * carried in the sequence's state slot; mixers and feed-forwards again come from b200q_layer_desc. */
 #define B200Q_ARCH_NORIDRA 3
+/* Paluzen: a layered decoder in sequential pre-norm form.  Every layer is
+ *   x <- x + a * mixer(shift(norm1 x)) (+ b * side_mixer(shift(norm1 x)));  x <- x + ff(norm2 x)
+ * with plain RMS norms (x / rms * w), an optional token shift of the mixer's input (a per-channel blend with
+ * the previous token's normed row, carried in the state slot), optional re-injection of the embedding output
+ * before a layer (x <- W_in [x; x0]), a tied output matrix and soft-capped logits. */
+#define B200Q_ARCH_PALUZEN 4
 
 #define B200Q_FORM_PARALLEL 0  /* x <- x + mixer(norm1 x) + ff(norm2 x)                                  */
 #define B200Q_FORM_POSTNORM 1  /* x <- norm1(alpha x + ls1 mixer(x~)); x <- norm2(alpha x + ls2 ff(x~)) */
+#define B200Q_FORM_PRENORM 2   /* x <- x + a mixer(h) (+ b side(h)), h = shift(norm1 x); x <- x + ff(norm2 x)     */
 
 #define B200Q_DTYPE_BF16 0
 #define B200Q_DTYPE_F32 1
@@ -438,11 +529,28 @@ typedef struct b200q_model_config {
 #define B200Q_MIXER_CHUNK_ATTN 4
 /* selective scan: per channel a [state_dim] fp32 state, S <- exp(dt A) S + dt x B, y = S.C + D x           */
 #define B200Q_MIXER_SELECTIVE_SCAN 5
+/* linear attention with a constant decay per head: q, k (heads x dim), v (heads x vdim) pass SiLU;
+ * S <- decay_h S + k v^T, o = S^T q; the concatenated heads take one RMS norm and a sigmoid gate              */
+#define B200Q_MIXER_LIGHTNING 6
+/* rotary grouped-query attention over a sliding window: keys (rotated) and values in a paged cache, the first
+ * rot_dims dimensions of every head turned in the half-split layout (i with i + rot_dims/2), a per-head score
+ * temperature, ordinary softmax, one sigmoid gate number per head                                              */
+#define B200Q_MIXER_WINDOW_ATTN 7
+/* time mixing with a data-dependent decay per key channel: r, k, v, gate and decay each read their own blend of
+ * the input with the previous token's input; w = exp(-exp(w0 + W2 tanh(W1 .))); o = (S + diag(u) k v^T)^T r,
+ * S <- diag(w) S + k v^T; per-head RMS, a weight, a SiLU gate                                                  */
+#define B200Q_MIXER_DECAY_MIX 8
 #define B200Q_FF_NONE 0
 #define B200Q_FF_POLYNORM 1         /* down(PolyNorm(up h))                                                          */
 #define B200Q_FF_MOE 2              /* top-k of clamped gated experts + an optional gated shared expert              */
 #define B200Q_FF_MOE_SIGMOID 3      /* top-k by sigmoid score, weights = the scores (not renormalised) applied to the
                                        expert's INPUT; expert = down(silu(gate h) * up h)                            */
+#define B200Q_FF_RELU2 4            /* down(relu(up h)^2)                                                            */
+/* top-k of relu^2 experts by softmax score over all experts: the choice adds a per-expert correction to the
+ * score and is limited to the best `keep_groups` of `n_groups` equal groups of neighbouring experts (a group's
+ * score = its largest choice score); weights = the chosen scores without correction, divided by their sum.  The
+ * last `n_identity` router outputs are identity experts: they return their input.                               */
+#define B200Q_FF_MOE_GROUPED 5
 
 typedef struct b200q_layer_desc {
   int32_t mixer;        /* B200Q_MIXER_*                                                               */
@@ -473,6 +581,19 @@ typedef struct b200q_layer_desc {
   int32_t inner;        /* selective scan: channels                                                       */
   int32_t state_dim;    /* selective scan: state size per channel                                         */
   int32_t dt_rank;      /* selective scan: rank of the step-size projection                               */
+  /* pre-norm form and mixers 6-8 (zero elsewhere) */
+  int32_t inject;       /* 1: before this layer x <- W_in [x; x0] ("inject" [W, 2W]; x0 = the embedding output) */
+  float mix_scale;      /* the mixer's output is multiplied by this (0 = 1)                               */
+  int32_t n_identity;   /* grouped mixture: identity experts behind the n_experts real ones               */
+  int32_t n_groups;     /* grouped mixture: groups of neighbouring experts (identity ones included)       */
+  int32_t keep_groups;  /* grouped mixture: groups a token may choose from                                */
+  /* a second mixer beside the first, reading the same input (weights "side.*"); 0 = none */
+  int32_t side_mixer;   /* B200Q_MIXER_LIGHTNING | B200Q_MIXER_DECAY_MIX                                  */
+  int32_t side_heads;
+  int32_t side_dim;
+  int32_t side_vdim;
+  int32_t side_decay_rank;
+  float side_scale;
 } b200q_layer_desc;
 
 typedef struct b200q_model* b200q_model_t;

@@ -23,12 +23,45 @@ int64_t al256(int64_t v) { return (v + 255) & ~(int64_t)255; }
 int esize(const b200q_model_config& c) { return c.dtype == B200Q_DTYPE_F32 ? 4 : 2; }
 int logit_rows(const b200q_model_config& c) { return std::max(c.max_logit_rows, c.max_seqs); }
 
+// the description of the mixer that stands beside a layer's first one, as a description of its own
+b200q_layer_desc side_desc(const b200q_layer_desc& d) {
+  b200q_layer_desc s{};
+  s.mixer = d.side_mixer;
+  s.heads = d.side_heads;
+  s.kv_heads = d.side_heads;
+  s.dim = d.side_dim;
+  s.vdim = d.side_vdim;
+  s.decay_rank = d.side_decay_rank;
+  s.mix_scale = d.side_scale;
+  s.kv_from = -1;
+  return s;
+}
+
+int check_sequence_mixer(int i, const b200q_layer_desc& d) {
+  if (d.mixer == B200Q_MIXER_LIGHTNING) {
+    B200Q_CHECK_ARG(d.heads > 0 && d.dim > 0 && d.dim <= 256 && d.vdim > 0, "layer %d: bad lightning sizes (dim <= 256)", i);
+  } else if (d.mixer == B200Q_MIXER_DECAY_MIX) {
+    B200Q_CHECK_ARG(d.heads > 0 && d.dim > 0 && d.dim <= 256 && d.vdim == d.dim && d.decay_rank > 0,
+                    "layer %d: bad decay-mix sizes (dim <= 256, values as wide as keys)", i);
+  } else {
+    B200Q_CHECK_ARG(d.heads > 0 && d.kv_heads > 0 && d.heads % d.kv_heads == 0 && d.dim > 0 && d.dim <= 512 &&
+                        d.vdim > 0 && d.vdim <= 512 && d.window >= 0 && d.rot_dims >= 0 && d.rot_dims % 2 == 0 &&
+                        d.rot_dims <= d.dim && (d.rot_dims == 0 || d.rot_base > 0.0),
+                    "layer %d: bad window-attention sizes (dim, vdim <= 512, even rot.dims <= dim, kv_heads divides heads)",
+                    i);
+  }
+  return B200Q_OK;
+}
+
 int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
   B200Q_CHECK_ARG(c && L, "layered config is null");
-  B200Q_CHECK_ARG(c->arch == B200Q_ARCH_RAMOPEL || c->arch == B200Q_ARCH_NORIDRA,
+  B200Q_CHECK_ARG(c->arch == B200Q_ARCH_RAMOPEL || c->arch == B200Q_ARCH_NORIDRA || c->arch == B200Q_ARCH_PALUZEN,
                   "create_layered: arch=%d is not a layered architecture", c->arch);
-  B200Q_CHECK_ARG(c->layer_form == B200Q_FORM_PARALLEL || c->layer_form == B200Q_FORM_POSTNORM, "layer_form=%d unknown",
-                  c->layer_form);
+  B200Q_CHECK_ARG(c->layer_form == B200Q_FORM_PARALLEL || c->layer_form == B200Q_FORM_POSTNORM ||
+                      c->layer_form == B200Q_FORM_PRENORM,
+                  "layer_form=%d unknown", c->layer_form);
+  B200Q_CHECK_ARG(c->logit_softcap >= 0.f && (c->token_shift == 0 || c->layer_form == B200Q_FORM_PRENORM),
+                  "bad logit soft cap, or a token shift outside the pre-norm form");
   B200Q_CHECK_ARG(c->norm_groups >= 0 && (c->norm_groups <= 1 || c->hidden % c->norm_groups == 0) &&
                       c->input_taps >= 0 && c->input_taps <= 16,
                   "bad norm groups (%d must divide the width %d) or input taps (%d, at most 16)", c->norm_groups,
@@ -66,11 +99,31 @@ int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
       B200Q_CHECK_ARG(d.inner > 0 && d.state_dim > 0 && d.state_dim <= 256 && d.dt_rank > 0 && d.conv_taps >= 1 &&
                           d.conv_taps <= 16,
                       "layer %d: bad selective-scan sizes (state <= 256, taps <= 16)", i);
+    } else if (d.mixer == B200Q_MIXER_LIGHTNING || d.mixer == B200Q_MIXER_DECAY_MIX ||
+               d.mixer == B200Q_MIXER_WINDOW_ATTN) {
+      if (int rc = check_sequence_mixer(i, d)) return rc;
     } else {
       set_error("layer %d: unknown mixer %d", i, d.mixer);
       return B200Q_EINVAL;
     }
-    if (d.ff == B200Q_FF_MOE_SIGMOID) {
+    if (d.side_mixer != 0) {
+      B200Q_CHECK_ARG(d.side_mixer == B200Q_MIXER_LIGHTNING || d.side_mixer == B200Q_MIXER_DECAY_MIX,
+                      "layer %d: side mixer %d is not one that can stand beside another", i, d.side_mixer);
+      if (int rc = check_sequence_mixer(i, side_desc(d))) return rc;
+    }
+    B200Q_CHECK_ARG((d.inject == 0 && d.side_mixer == 0 && d.mix_scale == 0.f) || c->layer_form == B200Q_FORM_PRENORM,
+                    "layer %d: re-injection, side mixers and mixer scales belong to the pre-norm form", i);
+    if (d.ff == B200Q_FF_RELU2) {
+      B200Q_CHECK_ARG(d.ff_dim > 0 && c->layer_form == B200Q_FORM_PRENORM, "layer %d: bad squared-ReLU feed-forward", i);
+    } else if (d.ff == B200Q_FF_MOE_GROUPED) {
+      const int E = d.n_experts + d.n_identity;
+      B200Q_CHECK_ARG(d.ff_dim > 0 && d.n_experts >= 0 && d.n_identity >= 0 && E > 0 && E <= 4096 && d.top_k > 0 &&
+                          d.top_k <= 32 && d.n_groups > 0 && d.n_groups <= 256 && E % d.n_groups == 0 &&
+                          d.keep_groups > 0 && d.keep_groups <= d.n_groups &&
+                          d.top_k <= d.keep_groups * (E / d.n_groups) && c->layer_form == B200Q_FORM_PRENORM,
+                      "layer %d: bad grouped mixture (experts + identity <= 4096, top <= 32, at most 256 groups that "
+                      "divide the experts, top fits the kept groups)", i);
+    } else if (d.ff == B200Q_FF_MOE_SIGMOID) {
       B200Q_CHECK_ARG(d.ff_dim > 0 && d.n_experts > 0 && d.n_experts <= 4096 && d.top_k > 0 && d.top_k <= 32 &&
                           d.top_k <= d.n_experts,
                       "layer %d: bad mixture sizes (experts <= 4096, top <= 32)", i);
@@ -91,9 +144,30 @@ int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
 // widest use of every workspace buffer over the layers
 struct Widths {
   int64_t proj = 1, cq = 1, q = 1, qa = 1, olat = 1, attn = 1, ffh = 1, ffa = 1, experts = 1, pairs = 1, egu = 1,
-          eact = 1, delta = 0, cvf = 0, baf = 0, dtr = 0, xc = 0, xp = 0;
-  bool moe = false, shared = false;
+          eact = 1, delta = 0, cvf = 0, baf = 0, dtr = 0, xc = 0, xp = 0, blend = 0;
+  bool moe = false, shared = false, hf = false, side = false, inject = false;
 };
+int64_t pad64(int64_t v) { return (v + 63) & ~(int64_t)63; }
+void sequence_mixer_widths(const b200q_layer_desc& d, int64_t W, Widths& w) {
+  const int64_t HD = (int64_t)d.heads * d.dim, HV = (int64_t)d.heads * d.vdim;
+  if (d.mixer == B200Q_MIXER_LIGHTNING) {
+    w.proj = std::max<int64_t>(w.proj, 2 * HD + 2 * HV);
+    w.cvf = std::max<int64_t>(w.cvf, 2 * HD + 2 * HV);  // q | k | v in fp32 and, behind them, the raw outputs
+    w.attn = std::max<int64_t>(w.attn, HV);
+  } else if (d.mixer == B200Q_MIXER_DECAY_MIX) {
+    w.hf = true;
+    w.blend = std::max<int64_t>(w.blend, 5 * W);
+    w.proj = std::max<int64_t>(w.proj, 4 * HD);
+    w.baf = std::max<int64_t>(w.baf, d.decay_rank);
+    w.cq = std::max<int64_t>(w.cq, d.decay_rank);
+    w.cvf = std::max<int64_t>(w.cvf, 5 * HD);  // r | k | v | w and the raw outputs
+    w.attn = std::max<int64_t>(w.attn, HD);
+  } else if (d.mixer == B200Q_MIXER_WINDOW_ATTN) {
+    w.proj = std::max<int64_t>(w.proj, pad64(HD + (int64_t)d.kv_heads * (d.dim + d.vdim) + d.heads));
+    w.qa = std::max<int64_t>(w.qa, HD);
+    w.attn = std::max<int64_t>(w.attn, HV);
+  }
+}
 Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_layer>& Ls) {
   Widths w;
   for (const auto& l : Ls) {
@@ -127,6 +201,21 @@ Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_la
       w.xp = std::max<int64_t>(w.xp, (d.dt_rank + 2 * (int64_t)d.state_dim + 63) & ~(int64_t)63);
       w.dtr = std::max<int64_t>(w.dtr, d.inner);
       w.attn = std::max<int64_t>(w.attn, d.inner);
+    } else {
+      sequence_mixer_widths(d, c.hidden, w);
+    }
+    if (d.side_mixer) {
+      w.side = true;
+      sequence_mixer_widths(side_desc(d), c.hidden, w);
+    }
+    if (d.inject) w.inject = true;
+    if (d.ff == B200Q_FF_RELU2) {
+      w.ffh = std::max<int64_t>(w.ffh, d.ff_dim);
+    } else if (d.ff == B200Q_FF_MOE_GROUPED) {
+      w.moe = true;
+      w.experts = std::max<int64_t>(w.experts, d.n_experts + d.n_identity);
+      w.pairs = std::max<int64_t>(w.pairs, d.top_k);
+      w.egu = std::max<int64_t>(w.egu, (int64_t)d.top_k * d.ff_dim);
     }
     if (d.ff == B200Q_FF_MOE_SIGMOID) {
       w.moe = true;
@@ -198,6 +287,12 @@ int64_t layout(b200q_model* m, uint8_t* base) {
   y->eout = take(w.moe ? T * w.pairs * W * es : 1);
   y->shout = take(w.shared ? T * W * es : 1);
   y->sgate = (float*)take(T * 4);
+  y->hf = (float*)take(w.hf ? T * W * 4 : 1);
+  y->x0 = (float*)take(w.inject ? T * W * 4 : 1);
+  y->cat = take(w.inject ? T * 2 * W * es : 1);
+  y->carry = (float*)take(c.token_shift ? (int64_t)c.max_seqs * W * 4 : 1);
+  y->mix2 = take(w.side ? T * W * es : 1);
+  y->blend = take(w.blend ? T * w.blend * es : 1);
   y->sel = take(LR * W * es);
   y->logits = (float*)take(LR * (int64_t)c.vocab * 4);
   y->logits_bf16 = take((int64_t)c.max_seqs * c.vocab * 2);
@@ -257,6 +352,39 @@ int layered_create(const b200q_model_config* cfg, const b200q_layer_desc* layers
       m->lay->state_slot_floats += (int64_t)l.d.inner * l.d.state_dim;
       l.conv_off = m->lay->state_slot_floats;
       m->lay->state_slot_floats += (int64_t)(l.d.conv_taps - 1) * l.d.inner;
+    } else if (l.d.mixer == B200Q_MIXER_WINDOW_ATTN) {
+      l.cache_block_off = m->lay->kv_block_bytes;
+      m->lay->kv_block_bytes += (int64_t)cfg->block_size * l.d.kv_heads * (l.d.dim + l.d.vdim) * es;
+      const int half = l.d.rot_dims / 2;
+      if (half > 0) {
+        std::vector<double> f(half);
+        for (int k = 0; k < half; ++k) f[k] = pow((double)l.d.rot_base, -2.0 * k / (double)l.d.rot_dims);
+        if (cudaMalloc(&l.freq, half * sizeof(double)) != cudaSuccess ||
+            cudaMemcpy(l.freq, f.data(), half * sizeof(double), cudaMemcpyHostToDevice) != cudaSuccess) {
+          set_error("create_layered: CUDA allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+          b200q_model_destroy(m);
+          return B200Q_ECUDA;
+        }
+      }
+    }
+    if (l.d.side_mixer) {
+      l.side.resize(1);
+      l.side[0].d = side_desc(l.d);
+    }
+    // recurrent mixers of the pre-norm form, first or side: the state, and for the decay mix the carried input
+    for (b200q_layered_layer* q : {&l, l.side.empty() ? (b200q_layered_layer*)nullptr : &l.side[0]}) {
+      if (!q || (q->d.mixer != B200Q_MIXER_LIGHTNING && q->d.mixer != B200Q_MIXER_DECAY_MIX)) continue;
+      m->lay->state_slot_floats = (m->lay->state_slot_floats + 3) & ~(int64_t)3;
+      q->state_off = m->lay->state_slot_floats;
+      m->lay->state_slot_floats += (int64_t)q->d.heads * q->d.dim * q->d.vdim;
+      if (q->d.mixer == B200Q_MIXER_DECAY_MIX) {
+        q->prev_off = m->lay->state_slot_floats;
+        m->lay->state_slot_floats += cfg->hidden;
+      }
+    }
+    if (cfg->token_shift) {
+      l.shift_off = m->lay->state_slot_floats;
+      m->lay->state_slot_floats += cfg->hidden;
     }
     if (cfg->layer_form == B200Q_FORM_POSTNORM && cfg->input_taps > 1) {
       // the last inputs of the two sublayers' input convolutions travel with the sequence
@@ -329,6 +457,43 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
   }
   FIELD("norm1", l.norm1, 1, W)
   if (d.ff != B200Q_FF_NONE) FIELD("norm2", l.norm2, 1, W)
+  if (c.token_shift) FIELD("shift", l.shift, 1, W)
+  if (d.inject) FIELD("inject", l.inject, W, 2 * W)
+  // the mixers of the pre-norm form, as a layer's first mixer ("mix.*") or beside it ("side.*")
+  for (int which = 0; which < 2; ++which) {
+    b200q_layered_layer* q = which == 0 ? &l : (l.side.empty() ? nullptr : &l.side[0]);
+    const char* pre = which == 0 ? "mix." : "side.";
+    if (!q || strncmp(field, pre, strlen(pre)) != 0) continue;
+    const char* f = field + strlen(pre);
+    const b200q_layer_desc& e = q->d;
+    const int64_t QD = (int64_t)e.heads * e.dim, QV = (int64_t)e.heads * e.vdim;
+#define SUB(fname, slot, r, cc)                          \
+  if (!strcmp(f, fname)) {                               \
+    if ((rc = expect((r), (cc)))) return rc;             \
+    *(const void**)&(slot) = p;                          \
+    return B200Q_OK;                                     \
+  }
+    if (e.mixer == B200Q_MIXER_LIGHTNING) {
+      SUB("proj", q->proj, 2 * QD + 2 * QV, W)
+      SUB("decay", q->head_decay, 1, e.heads)
+      SUB("out_norm", q->out_norm, 1, QV)
+      SUB("o", q->o, W, QV)
+    } else if (e.mixer == B200Q_MIXER_DECAY_MIX) {
+      SUB("mu", q->mu, 1, 5 * W)
+      SUB("proj", q->proj, 4 * QD, W)
+      SUB("w1", q->w1, e.decay_rank, W)
+      SUB("w2", q->w2, QD, e.decay_rank)
+      SUB("w0", q->w0, 1, QD)
+      SUB("bonus", q->bonus, 1, QD)
+      SUB("out_norm", q->out_norm, 1, QD)
+      SUB("o", q->o, W, QD)
+    } else if (e.mixer == B200Q_MIXER_WINDOW_ATTN) {
+      SUB("proj", q->proj, pad64(QD + (int64_t)e.kv_heads * (e.dim + e.vdim) + e.heads), W)
+      SUB("temp", q->temp, 1, e.heads)
+      SUB("o", q->o, W, QV)
+    }
+#undef SUB
+  }
   if (c.layer_form == B200Q_FORM_POSTNORM) {
     FIELD("ls1", l.ls1, 1, W)
     if (d.ff != B200Q_FF_NONE) FIELD("ls2", l.ls2, 1, W)
@@ -380,7 +545,17 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
     FIELD("mix.out_norm", l.out_norm, 1, HD)
     FIELD("mix.o", l.o, W, HD)
   }
-  if (d.ff == B200Q_FF_MOE_SIGMOID) {
+  if (d.ff == B200Q_FF_RELU2) {
+    FIELD("mlp.up", l.up, d.ff_dim, W)
+    FIELD("mlp.down", l.ff_down, W, d.ff_dim)
+  } else if (d.ff == B200Q_FF_MOE_GROUPED) {
+    FIELD("mlp.router", l.router, d.n_experts + d.n_identity, W)
+    FIELD("mlp.router_bias", l.router_bias, 1, d.n_experts + d.n_identity)
+    if (d.n_experts > 0) {
+      FIELD("mlp.experts_up", l.experts_up, (int64_t)d.n_experts * d.ff_dim, W)
+      FIELD("mlp.experts_down", l.experts_down, (int64_t)d.n_experts * W, d.ff_dim)
+    }
+  } else if (d.ff == B200Q_FF_MOE_SIGMOID) {
     FIELD("mlp.router", l.router, d.n_experts, W)
     FIELD("mlp.experts_gate_up", l.experts_gate_up, (int64_t)d.n_experts * 2 * d.ff_dim, W)
     FIELD("mlp.experts_down", l.experts_down, (int64_t)d.n_experts * W, d.ff_dim)
@@ -435,6 +610,28 @@ static int check_bound(b200q_model* m) {
       need_state = true;
       ok = ok && l.proj && l.conv_w && l.conv_b && l.x_proj && l.dt_proj && l.dt_b && l.a_log && l.dvec;
     }
+    if (m->cfg.token_shift) {
+      need_state = true;
+      ok = ok && l.shift;
+    }
+    if (d.inject) ok = ok && l.inject;
+    for (const b200q_layered_layer* q : {&l, l.side.empty() ? (const b200q_layered_layer*)nullptr : &l.side[0]}) {
+      if (!q) continue;
+      if (q != &l) ok = ok && q->o;
+      if (q->d.mixer == B200Q_MIXER_LIGHTNING) {
+        need_state = true;
+        ok = ok && q->proj && q->head_decay && q->out_norm;
+      } else if (q->d.mixer == B200Q_MIXER_DECAY_MIX) {
+        need_state = true;
+        ok = ok && q->mu && q->proj && q->w1 && q->w2 && q->w0 && q->bonus && q->out_norm;
+      } else if (q->d.mixer == B200Q_MIXER_WINDOW_ATTN) {
+        need_kv = true;
+        ok = ok && q->proj && q->temp;
+      }
+    }
+    if (d.ff == B200Q_FF_RELU2) ok = ok && l.up && l.ff_down;
+    if (d.ff == B200Q_FF_MOE_GROUPED)
+      ok = ok && l.router && l.router_bias && (d.n_experts == 0 || (l.experts_up && l.experts_down));
     if (d.ff == B200Q_FF_MOE_SIGMOID) ok = ok && l.router && l.experts_gate_up && l.experts_down;
     if (d.ff == B200Q_FF_POLYNORM) ok = ok && l.up && l.act && l.ff_down;
     if (d.ff == B200Q_FF_MOE)
@@ -485,7 +682,7 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
       b200q_linear((Aptr), (lda), (Wptr), (bias), (Cptr), (ldc), T, (N), (K), dt, (f32), stream))
   const int EW = B200Q_PROF_ELEMENTWISE;
 
-  const bool post = c.layer_form == B200Q_FORM_POSTNORM;
+  const bool post = c.layer_form == B200Q_FORM_POSTNORM, pre = c.layer_form == B200Q_FORM_PRENORM;
   const int groups = c.norm_groups > 0 ? c.norm_groups : 1;
   if (c.learned_pos)
     TRY(EW, (double)T * W * (2 * es + 4),
@@ -495,9 +692,68 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
         b200q_embed_f32(b->token_ids, b->prev_out_ids, m->embed, y->x, T, W, c.embed_scale > 0.f ? c.embed_scale : 1.f,
                         dt, stream));
 
+  // ---- mixers 6-8: read y->h1 [T, W] (model dtype; the decay mix reads the fp32 rows y->hf), write outp [T, W] ----
+  auto run_sequence_mixer = [&](const b200q_layered_layer& l, void* outp) -> int {
+    const b200q_layer_desc& d = l.d;
+    const int H = d.heads, HD = H * d.dim, HV = H * d.vdim;
+    if (d.mixer == B200Q_MIXER_LIGHTNING) {
+      const int NC = 2 * HD + HV, NP = NC + HV;
+      LIN(y->h1, W, l.proj, nullptr, y->proj, NP, NP, W, 0);  // [q | k | v | gate]
+      TRY(EW, (double)T * NC * (es + 4), b200q_act_to_f32(y->proj, NP, y->cvf, NC, NC, 1, T, dt, stream));
+      float* raw = y->cvf + (int64_t)T * NC;
+      TRY(B200Q_PROF_PREFILL_ATTN, 4.0 * T * H * (double)d.dim * d.vdim,
+          b200q_decay_attn(y->cvf, NC, 0, HD, 2 * HD, l.head_decay, nullptr, 0, nullptr, y->state + l.state_off,
+                           y->state_slot_floats, b->seq_desc, b->n_rows, H, d.dim, d.vdim, raw, stream));
+      TRY(EW, (double)T * HV * (4 + 2 * es),
+          b200q_gated_rmsnorm(raw, HV, HV, l.out_norm, (uint8_t*)y->proj + (size_t)NC * es, NP, 0, c.rms_eps, y->attn, T,
+                              dt, stream));
+      LIN(y->attn, HV, l.o, nullptr, outp, W, W, HV, 0);
+    } else if (d.mixer == B200Q_MIXER_DECAY_MIX) {
+      const int R = d.decay_rank, NQ = 4 * HD;
+      TRY(EW, (double)T * W * (4 + 5 * es),
+          b200q_shift_blend(y->hf, l.mu, 5, y->state + l.prev_off, y->state_slot_floats, b->seq_desc, b->row_seq, y->blend,
+                            T, W, dt, stream));
+      // every reader of the carried input has run: the last row of each portion takes its place
+      TRY(EW, 8.0 * b->n_rows * W,
+          b200q_store_carry(y->hf, 1, y->state + l.prev_off, y->state_slot_floats, b->seq_desc, b->n_rows, W, stream));
+      // r, k, v, gate: product g reads blend g (a column slice of the blend rows)
+      TRY(B200Q_PROF_GEMM, 2.0 * T * 4.0 * HD * W,
+          b200q_linear_batched(y->blend, 5 * W, W, l.proj, (long long)HD * W, y->proj, NQ, HD, T, HD, W, 4, dt, 0, stream));
+      LIN((uint8_t*)y->blend + (size_t)4 * W * es, 5 * W, l.w1, nullptr, y->baf, R, R, W, 1);
+      TRY(EW, (double)T * R * (4 + es), b200q_tanh_cast(y->baf, y->cq, (int64_t)T * R, dt, stream));
+      float* rkvw = y->cvf;  // [T, 4*HD] = r | k | v | w
+      LIN(y->cq, R, l.w2, nullptr, rkvw + 3 * HD, NQ, HD, R, 1);
+      TRY(EW, (double)T * HD * 8, b200q_decay_from_logits(rkvw + 3 * HD, NQ, l.w0, HD, T, dt, stream));
+      TRY(EW, (double)T * 3 * HD * (es + 4), b200q_act_to_f32(y->proj, NQ, rkvw, NQ, 3 * HD, 0, T, dt, stream));
+      float* raw = y->cvf + (int64_t)T * NQ;
+      TRY(B200Q_PROF_PREFILL_ATTN, 6.0 * T * H * (double)d.dim * d.dim,
+          b200q_decay_attn(rkvw, NQ, 0, HD, 2 * HD, nullptr, rkvw + 3 * HD, NQ, l.bonus, y->state + l.state_off,
+                           y->state_slot_floats, b->seq_desc, b->n_rows, H, d.dim, d.dim, raw, stream));
+      TRY(EW, (double)T * HD * (4 + 2 * es),
+          b200q_gated_rmsnorm(raw, HD, d.dim, l.out_norm, (uint8_t*)y->proj + (size_t)3 * HD * es, NQ, 1, c.rms_eps,
+                              y->attn, T, dt, stream));
+      LIN(y->attn, HD, l.o, nullptr, outp, W, W, HD, 0);
+    } else {  // B200Q_MIXER_WINDOW_ATTN
+      const int G = d.kv_heads, GD = G * d.dim, GV = G * d.vdim, NP = (int)pad64(HD + GD + GV + H);
+      uint8_t* cache = m->kv + m->num_blocks * l.cache_block_off;
+      LIN(y->h1, W, l.proj, nullptr, y->proj, NP, NP, W, 0);  // [q | k | v | gate number per head | zero rows]
+      TRY(EW, (double)T * ((HD + 2 * GD + 2 * GV) * es + HD * 4),
+          b200q_window_attn_prep(y->proj, NP, H, G, d.dim, d.vdim, d.rot_dims, l.freq, b->positions, b->slot_mapping,
+                                 l.temp, d.attn_scale, y->qa, cache, T, dt, stream));
+      TRY(B200Q_PROF_DECODE_ATTN, (double)b->sum_ctx_dec * (GD + GV) * es,
+          b200q_window_attn(y->qa, cache, b->block_table, b->bt_stride, b->row_seq, b->positions, b->seq_desc, b->n_rows,
+                            T, H, G, d.dim, d.vdim, c.block_size, d.window, (uint8_t*)y->proj + (size_t)(HD + GD + GV) * es,
+                            NP, y->attn, dt, stream));
+      LIN(y->attn, HV, l.o, nullptr, outp, W, W, HV, 0);
+    }
+    return B200Q_OK;
+  };
+
   // ---- the mixers: read y->h1 [T, W] (model dtype), write y->mix [T, W] ----
   auto run_mixer = [&](const b200q_layered_layer& l) -> int {
     const b200q_layer_desc& d = l.d;
+    if (d.mixer == B200Q_MIXER_LIGHTNING || d.mixer == B200Q_MIXER_DECAY_MIX || d.mixer == B200Q_MIXER_WINDOW_ATTN)
+      return run_sequence_mixer(l, y->mix);
     if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
       const int R = d.kv_rank, P = d.rot_dim, RP = R + P, H = d.heads, QD = d.dim + P;
       const bool own = d.kv_from < 0;
@@ -598,10 +854,71 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
     return B200Q_OK;
   };
 
+  bool keep_x0 = false;
+  for (const auto& l : y->layers) keep_x0 = keep_x0 || l.d.inject;
+  if (keep_x0) TRY(EW, 8.0 * T * W, b200q_copy_f32(y->x, y->x0, (int64_t)T * W, stream));
+
   for (int li = 0; li < c.n_layers; ++li) {
     const b200q_layered_layer& l = y->layers[li];
     const b200q_layer_desc& d = l.d;
     const bool has_ff = d.ff != B200Q_FF_NONE;
+    if (pre) {
+      // (x <- W_in [x; x0]);  x <- x + a mixer(h) (+ b side(h)), h = shift(norm1 x);  x <- x + ff(norm2 x)
+      if (d.inject) {
+        TRY(EW, (double)T * W * (8 + 2 * es), b200q_concat_cast(y->x, y->x0, y->cat, T, W, dt, stream));
+        LIN(y->cat, 2 * W, l.inject, nullptr, y->x, W, W, 2 * W, 1);
+      }
+      const bool side = !l.side.empty();
+      const bool want_f32 = d.mixer == B200Q_MIXER_DECAY_MIX || (side && l.side[0].d.mixer == B200Q_MIXER_DECAY_MIX);
+      TRY(EW, (double)T * W * (8 + es),
+          b200q_rmsnorm_shift(y->x, nullptr, l.norm1, c.token_shift ? l.shift : nullptr, y->state + l.shift_off,
+                              y->state_slot_floats, b->seq_desc, b->row_seq, b->n_rows, y->carry, y->h1,
+                              want_f32 ? y->hf : nullptr, T, W, c.rms_eps, dt, stream));
+      if (c.token_shift)
+        TRY(EW, 8.0 * b->n_rows * W,
+            b200q_store_carry(y->carry, 0, y->state + l.shift_off, y->state_slot_floats, b->seq_desc, b->n_rows, W, stream));
+      if ((rc = run_mixer(l))) return rc;
+      if (side && (rc = run_sequence_mixer(l.side[0], y->mix2))) return rc;
+      TRY(EW, (double)T * W * (8 + (side ? 2 : 1) * es),
+          b200q_residual_add(y->x, y->mix, d.mix_scale != 0.f ? d.mix_scale : 1.f, side ? y->mix2 : nullptr,
+                             side && l.side[0].d.mix_scale != 0.f ? l.side[0].d.mix_scale : 1.f, T, W, dt, stream));
+      if (has_ff) {
+        TRY(EW, (double)T * W * (4 + es),
+            b200q_rmsnorm_shift(y->x, nullptr, l.norm2, nullptr, nullptr, 0, nullptr, nullptr, 0, nullptr, y->h2, nullptr, T,
+                                W, c.rms_eps, dt, stream));
+        if (d.ff == B200Q_FF_RELU2) {
+          const int F = d.ff_dim;
+          LIN(y->h2, W, l.up, nullptr, y->ffh, F, F, W, 0);
+          TRY(EW, 2.0 * T * F * es, b200q_relu2(y->ffh, (int64_t)T * F, dt, stream));
+          LIN(y->ffh, F, l.ff_down, nullptr, y->ffo, W, W, F, 0);
+          TRY(EW, (double)T * W * (8 + es), b200q_residual_add(y->x, y->ffo, 1.f, nullptr, 0.f, T, W, dt, stream));
+        } else {
+          B200Q_CHECK_ARG(d.ff == B200Q_FF_MOE_GROUPED, "layer %d: feed-forward %d is not built for the pre-norm form", li,
+                          d.ff);
+          const int E = d.n_experts, ET = E + d.n_identity, K = d.top_k, F = d.ff_dim, P = T * K;
+          LIN(y->h2, W, l.router, nullptr, y->rlog, ET, ET, W, 1);
+          TRY(EW, (double)T * ET * 4,
+              b200q_moe_route_grouped(y->rlog, l.router_bias, T, ET, E, K, d.n_groups, d.keep_groups, y->idx, y->wts,
+                                      y->group_off, y->perm_tok, y->pair_pos, y->tile_tab, y->n_tiles, stream));
+          if (E > 0) {
+            const bool sorted = dt == B200Q_DTYPE_BF16 && W % 8 == 0;
+            if (sorted) TRY(EW, 2.0 * P * W * es, b200q_gather_rows(y->h2, y->perm_tok, y->esrc, P, W, stream));
+            TRY(B200Q_PROF_GEMM, 2.0 * P * (double)F * W,
+                b200q_linear_grouped(sorted ? y->esrc : y->h2, W, sorted ? nullptr : y->perm_tok, l.experts_up,
+                                     (long long)F * W, y->egu, F, y->group_off, E, P, F, W, dt, y->tile_tab, y->n_tiles,
+                                     stream));
+            TRY(EW, 2.0 * P * F * es, b200q_relu2(y->egu, (int64_t)P * F, dt, stream));
+            TRY(B200Q_PROF_GEMM, 2.0 * P * (double)F * W,
+                b200q_linear_grouped(y->egu, F, nullptr, l.experts_down, (long long)W * F, y->eout, W, y->group_off, E, P, W,
+                                     F, dt, y->tile_tab, y->n_tiles, stream));
+          }
+          TRY(EW, (double)T * W * (8 + (1 + K) * es),
+              b200q_residual_add_routed(y->x, y->eout, y->pair_pos, y->idx, y->wts, K, E, y->h2, T, W, dt, stream));
+        }
+      }
+      if (y->tap) TRY(EW, 8.0 * T * W, b200q_copy_f32(y->x, y->tap + (int64_t)li * T * W, (int64_t)T * W, stream));
+      continue;
+    }
     if (post) {
       // x <- norm1(alpha x + ls1 * mixer(x + conv1 x));  x <- norm2(alpha x + ls2 * ff(x + conv2 x))
       for (int sub = 0; sub < (has_ff ? 2 : 1); ++sub) {
@@ -684,12 +1001,18 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
       TRY(EW, (double)n * W * (4 + es),
           b200q_group_rmsnorm(y->x, b->sample_rows, nullptr, nullptr, 0, nullptr, 1.f, (const float*)m->final_norm, groups,
                               c.rms_eps, nullptr, y->sel, n, W, dt, stream));
+    else if (pre)
+      TRY(EW, (double)n * W * (4 + es),
+          b200q_rmsnorm_shift(y->x, b->sample_rows, (const float*)m->final_norm, nullptr, nullptr, 0, nullptr, nullptr, 0,
+                              nullptr, y->sel, nullptr, n, W, c.rms_eps, dt, stream));
     else
       TRY(EW, (double)n * W * (4 + es),
           b200q_centered_rmsnorm(y->x, b->sample_rows, (const float*)m->final_norm, nullptr, y->sel, nullptr, n, W,
                                  c.rms_eps, dt, stream));
     TRY(B200Q_PROF_GEMM, 2.0 * n * (double)c.vocab * W,
         b200q_linear(y->sel, W, m->lm_head, nullptr, y->logits, c.vocab, n, c.vocab, W, dt, 1, stream));
+    if (c.logit_softcap > 0.f)
+      TRY(EW, 8.0 * n * c.vocab, b200q_softcap_f32(y->logits, (int64_t)n * c.vocab, c.logit_softcap, stream));
     if (!b->no_sampling) {
       if (b->sample_params) {
         TRY(EW, 6.0 * n * c.vocab, b200q_f32_to_bf16(y->logits, y->logits_bf16, (int64_t)n * c.vocab, stream));

@@ -34,6 +34,14 @@ struct b200q_layered_layer {
   const float *conv_w = nullptr, *conv_b = nullptr, *a_log = nullptr, *dt_bias = nullptr, *r1 = nullptr, *r2 = nullptr;
   const void *x_proj = nullptr, *dt_proj = nullptr;
   const float *dt_b = nullptr, *dvec = nullptr;
+  // pre-norm form: token-shift weights and the re-injection matrix; lightning (proj = [q | k | v | gate] rows,
+  // head_decay), window attention (proj = [q | k | v | gate number per head] rows, temp), decay mix (mu: five
+  // blend weights; proj = [r | k | v | gate] rows, each product reading its own blend; w1, w2, w0: the decay's
+  // low-rank path; bonus)
+  const float *shift = nullptr, *head_decay = nullptr, *temp = nullptr, *mu = nullptr, *bonus = nullptr;
+  const void *inject = nullptr, *w1 = nullptr, *experts_up = nullptr;
+  std::vector<b200q_layered_layer> side;  // the mixer beside the first one (none or one)
+  int64_t shift_off = 0, prev_off = 0;    // floats into a state slot: carried normed row, carried mixer input
   int64_t cache_block_off = 0;  // bytes per block of the cache regions before this layer's (own cache only)
   int64_t state_off = 0;        // floats into a state slot: the recurrent state
   int64_t conv_off = 0, canon1_off = 0, canon2_off = 0;  // ... the carried inputs of the convolutions
@@ -60,6 +68,9 @@ struct b200q_layered {
   int32_t *idx = nullptr, *group_off = nullptr, *perm_tok = nullptr, *pair_pos = nullptr, *tile_tab = nullptr,
           *n_tiles = nullptr;
   void* esrc = nullptr;  // the routed pairs' inputs gathered into expert order (bf16 path)
+  // pre-norm form: fp32 mixer input, embedding output, carried rows of a step, side mixer's output, [x | x0], blends
+  float *hf = nullptr, *x0 = nullptr, *carry = nullptr;
+  void *mix2 = nullptr, *cat = nullptr, *blend = nullptr;
 };
 
 struct b200q_layer {

@@ -55,6 +55,8 @@ class ModelConfig(C.Structure):
         ("residual_alpha", C.c_float),
         ("input_taps", C.c_int32),
         ("learned_pos", C.c_int32),
+        ("token_shift", C.c_int32),
+        ("logit_softcap", C.c_float),
     ]
 
 
@@ -62,8 +64,10 @@ ARCH_LLAMA = 0
 ARCH_GEMMA2 = 1
 ARCH_RAMOPEL = 2
 ARCH_NORIDRA = 3
+ARCH_PALUZEN = 4
 FORM_PARALLEL = 0
 FORM_POSTNORM = 1
+FORM_PRENORM = 2
 DTYPE_BF16 = 0
 DTYPE_F32 = 1
 MIXER_LATENT_ATTN = 1
@@ -71,10 +75,15 @@ MIXER_GENERAL_DELTA = 2
 MIXER_GATED_DELTA = 3
 MIXER_CHUNK_ATTN = 4
 MIXER_SELECTIVE_SCAN = 5
+MIXER_LIGHTNING = 6
+MIXER_WINDOW_ATTN = 7
+MIXER_DECAY_MIX = 8
 FF_NONE = 0
 FF_POLYNORM = 1
 FF_MOE = 2
 FF_MOE_SIGMOID = 3
+FF_RELU2 = 4
+FF_MOE_GROUPED = 5
 
 
 class LayerDesc(C.Structure):
@@ -86,6 +95,9 @@ class LayerDesc(C.Structure):
         ("top_k", C.c_int32), ("expert_limit", C.c_float), ("shared_dim", C.c_int32), ("shared_limit", C.c_float),
         ("kv_heads", C.c_int32), ("conv_taps", C.c_int32), ("softcap", C.c_float), ("chunk", C.c_int32),
         ("inner", C.c_int32), ("state_dim", C.c_int32), ("dt_rank", C.c_int32),
+        ("inject", C.c_int32), ("mix_scale", C.c_float), ("n_identity", C.c_int32), ("n_groups", C.c_int32),
+        ("keep_groups", C.c_int32), ("side_mixer", C.c_int32), ("side_heads", C.c_int32), ("side_dim", C.c_int32),
+        ("side_vdim", C.c_int32), ("side_decay_rank", C.c_int32), ("side_scale", C.c_float),
     ]
 
 
@@ -216,6 +228,23 @@ SIGNATURES = {
     "b200q_silu_glu": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
     "b200q_layer_sum": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp]),
     "b200q_argmax_f32": (_i, [_vp, _vp, _i, _i, _vp]),
+    # pre-norm layers, token shift, mixers 6-8
+    "b200q_rmsnorm_shift": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "b200q_store_carry": (_i, [_vp, _i, _vp, _ll, _vp, _i, _i, _vp]),
+    "b200q_shift_blend": (_i, [_vp, _vp, _i, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200q_relu2": (_i, [_vp, _i64, _i, _vp]),
+    "b200q_tanh_cast": (_i, [_vp, _vp, _i64, _i, _vp]),
+    "b200q_act_to_f32": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b200q_decay_from_logits": (_i, [_vp, _i, _vp, _i, _i, _i, _vp]),
+    "b200q_decay_attn": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "b200q_gated_rmsnorm": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _f, _vp, _i, _i, _vp]),
+    "b200q_window_attn_prep": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp]),
+    "b200q_window_attn": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _i, _vp]),
+    "b200q_moe_route_grouped": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_residual_add": (_i, [_vp, _vp, _f, _vp, _f, _i, _i, _i, _vp]),
+    "b200q_residual_add_routed": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _vp]),
+    "b200q_concat_cast": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200q_softcap_f32": (_i, [_vp, _i64, _f, _vp]),
     "b200q_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "b200q_copy_f32": (_i, [_vp, _vp, _i64, _vp]),
     "b200q_model_create_layered": (_i, [C.POINTER(ModelConfig), C.POINTER(LayerDesc), C.POINTER(_vp)]),

@@ -17,7 +17,7 @@ from typing import Dict, Iterable, List, Optional, Tuple
 import torch
 
 from . import lib as L
-from . import noridra, ramopel
+from . import noridra, paluzen, ramopel
 
 BLOCK_SIZE = 16
 
@@ -189,9 +189,10 @@ GEMMA_2_2B = ModelSpec(hidden=2304, n_layers=26, n_q_heads=8, n_kv_heads=4, head
                        attn_softcap=50.0, final_softcap=30.0, sliding_window=4096)
 BUILTIN_SPECS = {"llama-3-8b": LLAMA_3_8B, "llama-3.2-1b": LLAMA_32_1B,
                  "gemma-2-9b": GEMMA_2_9B, "gemma-2-2b": GEMMA_2_2B, **ramopel.BUILTIN_SPECS,
-                 **noridra.BUILTIN_SPECS}
+                 **noridra.BUILTIN_SPECS, **paluzen.BUILTIN_SPECS}
 # config.json "architecture" -> the module that reads it (layered designs; HF-style configs carry "architectures")
-LAYERED_DESIGNS = {ramopel.ARCHITECTURE: ramopel.RamopelSpec, noridra.ARCHITECTURE: noridra.NoridraSpec}
+LAYERED_DESIGNS = {ramopel.ARCHITECTURE: ramopel.RamopelSpec, noridra.ARCHITECTURE: noridra.NoridraSpec,
+                   paluzen.ARCHITECTURE: paluzen.PaluzenSpec}
 
 
 def rope_table(max_pos: int, head_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
@@ -394,7 +395,7 @@ class NativeModel:
         torch.cuda.synchronize(self.device)
 
     def _init_layered(self, weights, max_tokens, max_seqs, num_blocks, gpu_memory_utilization, max_logit_rows):
-        """a layered architecture (Ramopel, Noridra): one b200q_layer_desc per layer, a paged cache for the
+        """a layered architecture (Ramopel, Noridra, Paluzen): one b200q_layer_desc per layer, a paged cache for the
         attention layers that own one, and one fp32 state slot per live sequence (recurrent states and the
         carried inputs of convolutions)"""
         spec, lib = self.spec, self.lib
@@ -411,14 +412,20 @@ class NativeModel:
         L.check(lib.b200q_model_create_layered(C.byref(self.cfg), descs, C.byref(h)))
         self.handle = h
         self._keep: List[torch.Tensor] = []
-        for name, t in weights:
-            # 2-D: a matrix, in the model's dtype; 1-D: a vector or constants, as one fp32 row
-            if t.dim() == 2:
-                t = t.to(device=self.device, dtype=self.dtype).contiguous()
+        uploaded = {}   # id of a source tensor -> (source, device copy): a tensor yielded under several names
+        for name, src in weights:   # (tied matrices, layers that run more than once) is uploaded once
+            if id(src) in uploaded:
+                t = uploaded[id(src)][1]
             else:
-                t = t.reshape(1, -1).to(device=self.device, dtype=torch.float32).contiguous()
-            self._keep.append(t)
+                # 2-D: a matrix, in the model's dtype; 1-D: a vector or constants, as one fp32 row
+                if src.dim() == 2:
+                    t = src.to(device=self.device, dtype=self.dtype).contiguous()
+                else:
+                    t = src.reshape(1, -1).to(device=self.device, dtype=torch.float32).contiguous()
+                uploaded[id(src)] = (src, t)
+                self._keep.append(t)
             L.check(lib.b200q_model_bind_weight(h, name.encode(), t.data_ptr(), t.shape[0], t.shape[1]))
+        del uploaded
         ws_bytes = int(lib.b200q_model_workspace_bytes_of(h))
         if ws_bytes <= 0:
             raise L.B200QError(ws_bytes, "workspace sizing failed")
