@@ -145,6 +145,368 @@ __global__ void __launch_bounds__(256) window_attn_kernel(const float* __restric
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// window attention on the tensor cores (bf16 cache; key and value head sizes of 64 or 128).  One CTA per
+// (sequence of the step, key/value head, tile of 16 consecutive tokens of the sequence's portion); warp w serves
+// query head w of the group, the 16 tokens are the M rows of mma.sync.m16n8k16 tiles.  Tiles of 64 cached rows
+// (keys and values) arrive by cp.async into double-buffered shared memory that all heads of the group read:
+// the keys through ldmatrix (S = Q K^T), the values through ldmatrix.trans (O += P V).  Online softmax in fp32
+// registers; the weights are rounded to bf16 before they are summed, as the value product sees them.  Key tiles
+// start at the first key the tile's first token sees.
+// ------------------------------------------------------------------------------------------------
+constexpr int WATT_KEYS = 64;
+constexpr float WATT_NEG = -1e30f;  // finite floor of the running maximum: exp(masked - floor) = 0, never NaN
+template <int D, int DV>
+__global__ void __launch_bounds__(256) window_attn_mma_kernel(const float* __restrict__ qs, const bf16* __restrict__ cache,
+                                                              const int32_t* __restrict__ block_table, int bt_stride,
+                                                              const int32_t* __restrict__ seq_desc, int heads,
+                                                              int kv_heads, int block_size, int window,
+                                                              const bf16* __restrict__ gate, int ld_gate,
+                                                              bf16* __restrict__ out, int skip_single) {
+  constexpr int LDK = D + 8, LDV = DV + 8;  // padded rows (bf16 elements): ldmatrix rows fall on different banks
+  extern __shared__ __align__(16) uint8_t smraw[];
+  const int nw = blockDim.x >> 5;
+  bf16* qsm = reinterpret_cast<bf16*>(smraw);       // [nw][16][LDK]
+  bf16* kbuf = qsm + (long long)nw * 16 * LDK;      // [2][64][LDK]
+  bf16* vbuf = kbuf + 2 * WATT_KEYS * LDK;          // [2][64][LDV]
+  const SeqView sq = seq_view(seq_desc, blockIdx.x);
+  const int r0 = blockIdx.z * 16;
+  if (r0 >= sq.n || (skip_single && sq.n == 1)) return;  // single tokens: the decode kernel's
+  const int nrows = min(16, sq.n - r0);
+  const int rep = heads / kv_heads, parts = (rep + nw - 1) / nw;
+  const int g = blockIdx.y / parts, part = blockIdx.y % parts;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q4 = lane & 3;
+  const int hg = part * nw + warp;
+  const bool live = hg < rep;
+  const int h = g * rep + (live ? hg : 0);
+  const int p_first = sq.pos0 + r0, p_last = p_first + nrows - 1;
+  const int lo_first = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int32_t* bt = block_table + (long long)blockIdx.x * bt_stride;
+  const int GD = kv_heads * D, RS = GD + kv_heads * DV;
+  const int ntiles = (p_last - lo_first) / WATT_KEYS + 1;
+
+  auto load_tile = [&](int c, int buf) {
+    const int j0 = lo_first + c * WATT_KEYS;
+    bf16* kb = kbuf + (long long)buf * WATT_KEYS * LDK;
+    bf16* vb = vbuf + (long long)buf * WATT_KEYS * LDV;
+    constexpr int CK = D / 8, CV = DV / 8, CPR = CK + CV;  // 16-byte pieces of a cached row's key and value
+    for (int e = tid; e < WATT_KEYS * CPR; e += blockDim.x) {
+      const int j = e / CPR, ck = e % CPR, pos = j0 + j;
+      bf16* dst = ck < CK ? kb + j * LDK + ck * 8 : vb + j * LDV + (ck - CK) * 8;
+      if (pos <= p_last) {
+        const long long row = (long long)bt[pos / block_size] * block_size + pos % block_size;
+        const bf16* src = ck < CK ? cache + row * RS + (long long)g * D + ck * 8
+                                  : cache + row * RS + GD + (long long)g * DV + (ck - CK) * 8;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  load_tile(0, 0);
+  // the queries of this CTA's heads (scale and temperature folded in), bf16, rows past the portion are zeros
+  for (int e = tid; e < nw * 16 * D; e += blockDim.x) {
+    const int w = e / (16 * D), r = (e / D) % 16, d = e % D, hh = part * nw + w;
+    const float v = (hh < rep && r < nrows) ? qs[((long long)(sq.row0 + r0 + r) * heads + g * rep + hh) * D + d] : 0.f;
+    qsm[((long long)w * 16 + r) * LDK + d] = __float2bfloat16_rn(v);
+  }
+  const uint32_t q_s = smem_u32(qsm + (long long)warp * 16 * LDK);
+  const uint32_t a_off = (uint32_t)(((lane & 15) * LDK + (lane >> 4) * 8) * 2);
+  const uint32_t kq_off = (uint32_t)((((lane & 7) + 8 * (lane >> 4)) * LDK + 8 * ((lane >> 3) & 1)) * 2);
+  // rows gq and gq + 8 of the tile belong to this thread
+  int p_row[2], lo_row[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = gq + 8 * r;
+    p_row[r] = i < nrows ? p_first + i : -1;  // a dead row sees no key
+    lo_row[r] = (window > 0 && i < nrows) ? max(0, p_row[r] - window + 1) : 0;
+  }
+  float m_[2] = {WATT_NEG, WATT_NEG}, l_[2] = {0.f, 0.f};
+  float o[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int c = 0; c < ntiles; ++c) {
+    const int buf = c & 1, j0 = lo_first + c * WATT_KEYS;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // tile c (and, first time, the queries) is in shared memory; tile c-1 is done with
+    if (c + 1 < ntiles) load_tile(c + 1, buf ^ 1);
+    if (!live) continue;
+    const uint32_t kb_s = smem_u32(kbuf + (long long)buf * WATT_KEYS * LDK);
+    const uint32_t vb_s = smem_u32(vbuf + (long long)buf * WATT_KEYS * LDV);
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldsm_x4(q_s + a_off + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+      for (int nt2 = 0; nt2 < 4; ++nt2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(kb_s + kq_off + (uint32_t)(nt2 * 16 * LDK * 2 + ks * 32), b0, b1, b2, b3);
+        mma_bf16_16816(s[2 * nt2], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(s[2 * nt2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    float rmax[2] = {WATT_NEG, WATT_NEG};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + nt * 8 + 2 * q4 + (e & 1), r = e >> 1;
+        const float v = (j <= p_row[r] && j >= lo_row[r]) ? s[nt][e] : -INFINITY;
+        s[nt][e] = v;
+        rmax[r] = fmaxf(rmax[r], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 1));
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 2));
+      const float mn = fmaxf(m_[r], rmax[r]);
+      corr[r] = __expf(m_[r] - mn);
+      m_[r] = mn;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = round_bf16(__expf(s[nt][e] - m_[e >> 1]));  // masked: exp(-inf) = 0
+        s[nt][e] = pv;
+        psum[e >> 1] += pv;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_[r] = l_[r] * corr[r] + psum[r];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk2 = 0; kk2 < WATT_KEYS / 16; ++kk2) {
+      const uint32_t a0 = pack_bf16x2(s[2 * kk2][0], s[2 * kk2][1]), a1 = pack_bf16x2(s[2 * kk2][2], s[2 * kk2][3]);
+      const uint32_t a2 = pack_bf16x2(s[2 * kk2 + 1][0], s[2 * kk2 + 1][1]),
+                     a3 = pack_bf16x2(s[2 * kk2 + 1][2], s[2 * kk2 + 1][3]);
+      const int key = kk2 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const uint32_t v_row = vb_s + (uint32_t)((key * LDV + 8 * (lane >> 4)) * 2);
+#pragma unroll
+      for (int nd2 = 0; nd2 < DV / 16; ++nd2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(v_row + nd2 * 32, b0, b1, b2, b3);
+        mma_bf16_16816(o[2 * nd2], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(o[2 * nd2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+  }
+  if (!live) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_[r] += __shfl_xor_sync(0xffffffffu, l_[r], 1);
+    l_[r] += __shfl_xor_sync(0xffffffffu, l_[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = gq + 8 * r;
+    if (i >= nrows) continue;
+    const long long t = sq.row0 + r0 + i;
+    const float gv = gate ? sigmoidf_(__bfloat162float(gate[t * ld_gate + h])) : 1.f;
+    const float inv = gv / l_[r];
+    bf16* orow = out + (t * heads + h) * DV;
+#pragma unroll
+    for (int nt = 0; nt < DV / 8; ++nt) {
+      const int d = nt * 8 + 2 * q4;
+      *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16x2(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same for a single decoded token of a sequence: one CTA (4 warps) per (sequence, key/value head).  The M
+// rows of the tiles are the query heads of the group (<= 16), so one pass over the cached rows serves all of
+// them; warp w takes the 32-key tiles w, w+4, ... of the token's window through its own double-buffered
+// cp.async ring (no CTA barrier inside the loop) and keeps its own softmax state; the four states are merged
+// through shared memory in a fixed order at the end.
+// ------------------------------------------------------------------------------------------------
+constexpr int WDEC_KEYS = 32, WDEC_WARPS = 4;
+template <int D, int DV>
+__global__ void __launch_bounds__(128) window_attn_decode_mma_kernel(const float* __restrict__ qs,
+                                                                     const bf16* __restrict__ cache,
+                                                                     const int32_t* __restrict__ block_table,
+                                                                     int bt_stride, const int32_t* __restrict__ seq_desc,
+                                                                     int heads, int kv_heads, int block_size, int window,
+                                                                     const bf16* __restrict__ gate, int ld_gate,
+                                                                     bf16* __restrict__ out) {
+  constexpr int LDK = D + 8, LDV = DV + 8, MS = DV + 2;
+  extern __shared__ __align__(16) uint8_t smraw[];
+  bf16* qsm = reinterpret_cast<bf16*>(smraw);    // [16][LDK]
+  bf16* kvbuf = qsm + 16 * LDK;                  // [4 warps][2][32][LDK + LDV]
+  float* mrg = reinterpret_cast<float*>(kvbuf);  // after the loop: [4][16][DV + 2]
+  const SeqView sq = seq_view(seq_desc, blockIdx.x);
+  if (sq.n != 1) return;  // portions of prompts take the tile kernel
+  const int g = blockIdx.y, rep = heads / kv_heads;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q4 = lane & 3;
+  const int p = sq.pos0, lo = window > 0 ? max(0, p - window + 1) : 0;
+  const long long t = sq.row0;
+  const int32_t* bt = block_table + (long long)blockIdx.x * bt_stride;
+  const int GD = kv_heads * D, RS = GD + kv_heads * DV;
+  const int ntiles = (p - lo) / WDEC_KEYS + 1;
+  bf16* kw = kvbuf + (long long)warp * 2 * WDEC_KEYS * (LDK + LDV);
+
+  auto load_tile = [&](int c, int buf) {  // by this warp alone
+    const int j0 = lo + c * WDEC_KEYS;
+    bf16* kb = kw + (long long)buf * WDEC_KEYS * (LDK + LDV);
+    bf16* vb = kb + WDEC_KEYS * LDK;
+    constexpr int CK = D / 8, CV = DV / 8, CPR = CK + CV;
+    for (int e = lane; e < WDEC_KEYS * CPR; e += 32) {
+      const int j = e / CPR, ck = e % CPR, pos = j0 + j;
+      bf16* dst = ck < CK ? kb + j * LDK + ck * 8 : vb + j * LDV + (ck - CK) * 8;
+      if (pos <= p) {
+        const long long row = (long long)bt[pos / block_size] * block_size + pos % block_size;
+        const bf16* src = ck < CK ? cache + row * RS + (long long)g * D + ck * 8
+                                  : cache + row * RS + GD + (long long)g * DV + (ck - CK) * 8;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (warp < ntiles) load_tile(warp, 0);
+  for (int e = tid; e < 16 * D; e += blockDim.x) {
+    const int r = e / D, d = e % D;
+    qsm[r * LDK + d] = __float2bfloat16_rn(r < rep ? qs[(t * heads + g * rep + r) * D + d] : 0.f);
+  }
+  __syncthreads();
+  const uint32_t q_s = smem_u32(qsm);
+  const uint32_t a_off = (uint32_t)(((lane & 15) * LDK + (lane >> 4) * 8) * 2);
+  const uint32_t kq_off = (uint32_t)((((lane & 7) + 8 * (lane >> 4)) * LDK + 8 * ((lane >> 3) & 1)) * 2);
+  const bool row_on[2] = {gq < rep, gq + 8 < rep};
+  float m_[2] = {WATT_NEG, WATT_NEG}, l_[2] = {0.f, 0.f};
+  float o[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int c = warp, it = 0; c < ntiles; c += WDEC_WARPS, ++it) {
+    const int buf = it & 1, j0 = lo + c * WDEC_KEYS;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    if (c + WDEC_WARPS < ntiles) load_tile(c + WDEC_WARPS, buf ^ 1);
+    const bf16* kb = kw + (long long)buf * WDEC_KEYS * (LDK + LDV);
+    const uint32_t kb_s = smem_u32(kb), vb_s = smem_u32(kb + WDEC_KEYS * LDK);
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldsm_x4(q_s + a_off + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+      for (int nt2 = 0; nt2 < 2; ++nt2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(kb_s + kq_off + (uint32_t)(nt2 * 16 * LDK * 2 + ks * 32), b0, b1, b2, b3);
+        mma_bf16_16816(s[2 * nt2], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(s[2 * nt2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    float rmax[2] = {WATT_NEG, WATT_NEG};
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + nt * 8 + 2 * q4 + (e & 1), r = e >> 1;
+        const float v = (row_on[r] && j <= p) ? s[nt][e] : -INFINITY;  // tiles start at the window's first key
+        s[nt][e] = v;
+        rmax[r] = fmaxf(rmax[r], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 1));
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 2));
+      const float mn = fmaxf(m_[r], rmax[r]);
+      corr[r] = __expf(m_[r] - mn);
+      m_[r] = mn;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = round_bf16(__expf(s[nt][e] - m_[e >> 1]));
+        s[nt][e] = pv;
+        psum[e >> 1] += pv;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_[r] = l_[r] * corr[r] + psum[r];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk2 = 0; kk2 < WDEC_KEYS / 16; ++kk2) {
+      const uint32_t a0 = pack_bf16x2(s[2 * kk2][0], s[2 * kk2][1]), a1 = pack_bf16x2(s[2 * kk2][2], s[2 * kk2][3]);
+      const uint32_t a2 = pack_bf16x2(s[2 * kk2 + 1][0], s[2 * kk2 + 1][1]),
+                     a3 = pack_bf16x2(s[2 * kk2 + 1][2], s[2 * kk2 + 1][3]);
+      const int key = kk2 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const uint32_t v_row = vb_s + (uint32_t)((key * LDV + 8 * (lane >> 4)) * 2);
+#pragma unroll
+      for (int nd2 = 0; nd2 < DV / 16; ++nd2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(v_row + nd2 * 32, b0, b1, b2, b3);
+        mma_bf16_16816(o[2 * nd2], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(o[2 * nd2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+  }
+  // ---- merge the four warps' states: [warp][row][DV + 2] = (o..., m, l); a warp without tiles holds (0, floor, 0) ----
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_[r] += __shfl_xor_sync(0xffffffffu, l_[r], 1);
+    l_[r] += __shfl_xor_sync(0xffffffffu, l_[r], 2);
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();  // every warp is done with its buffers: they become the merge area
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float* dst = mrg + ((long long)warp * 16 + gq + 8 * r) * MS;
+#pragma unroll
+    for (int nt = 0; nt < DV / 8; ++nt) {
+      dst[nt * 8 + 2 * q4] = o[nt][2 * r];
+      dst[nt * 8 + 2 * q4 + 1] = o[nt][2 * r + 1];
+    }
+    if (q4 == 0) {
+      dst[DV] = m_[r];
+      dst[DV + 1] = l_[r];
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < rep * DV; e += blockDim.x) {
+    const int r = e / DV, d = e % DV;
+    float mx = WATT_NEG;
+#pragma unroll
+    for (int w = 0; w < WDEC_WARPS; ++w) mx = fmaxf(mx, mrg[((long long)w * 16 + r) * MS + DV]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < WDEC_WARPS; ++w) {
+      const float* src = mrg + ((long long)w * 16 + r) * MS;
+      const float f = expf(src[DV] - mx);
+      num = fmaf(src[d], f, num);
+      den = fmaf(src[DV + 1], f, den);
+    }
+    const int h = g * rep + r;
+    const float gv = gate ? sigmoidf_(__bfloat162float(gate[t * ld_gate + h])) : 1.f;
+    out[(t * heads + h) * DV + d] = __float2bfloat16_rn(num / den * gv);
+  }
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -168,6 +530,14 @@ int b200q_window_attn_prep(const void* proj, int ldp, int heads, int kv_heads, i
   return B200Q_OK;
 }
 
+static int window_attn_mma_mode() {  // B200Q_WINDOW_ATTN_MMA=0: the scalar kernel everywhere
+  static const int mode = [] {
+    const char* v = getenv("B200Q_WINDOW_ATTN_MMA");
+    return v ? atoi(v) : 1;
+  }();
+  return mode;
+}
+
 int b200q_window_attn(const float* qs, const void* cache, const int32_t* block_table, int bt_stride, const int32_t* row_seq,
                       const int32_t* positions, const int32_t* seq_desc, int n_seqs, int T_, int heads, int kv_heads,
                       int dim, int vdim, int block_size, int window, const void* gate, int ld_gate, void* out, int dtype,
@@ -180,6 +550,48 @@ int b200q_window_attn(const float* qs, const void* cache, const int32_t* block_t
   if (T_ == 0) return B200Q_OK;
   cudaStream_t st = as_stream(stream);
   const int rep = heads / kv_heads;
+  // bf16 caches with head sizes the tensor-core tiles take, when the caller gives the per-sequence view
+  if (seq_desc && n_seqs > 0 && dtype == B200Q_DTYPE_BF16 && (dim == 64 || dim == 128) && (vdim == 64 || vdim == 128) &&
+      window_attn_mma_mode() && ((reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    const int nw = rep < 8 ? rep : 8, parts = (rep + nw - 1) / nw;
+    const int ztiles = (T_ - n_seqs + 1 + 15) / 16;  // no portion of this step is longer than T - (n_seqs - 1)
+    dim3 mgrid(n_seqs, kv_heads * parts, ztiles);
+    B200Q_CHECK_ARG(mgrid.y <= 65535 && mgrid.z <= 65535, "window_attn: step too large (%d tokens)", T_);
+    const size_t msm = ((size_t)nw * 16 + 2 * WATT_KEYS) * (dim + 8) * 2 + (size_t)2 * WATT_KEYS * (vdim + 8) * 2;
+    // single decoded tokens go to the kernel whose rows are the heads of a group (groups of up to 16 heads); a
+    // step of single tokens only (T == n_seqs) needs no tile kernel
+    const bool dec = rep <= 16, tiles = !dec || T_ > n_seqs;
+    const size_t dsm = std::max((size_t)16 * (dim + 8) * 2 + (size_t)WDEC_WARPS * 2 * WDEC_KEYS * (dim + vdim + 16) * 2,
+                                (size_t)16 * (dim + 8) * 2 + (size_t)WDEC_WARPS * 16 * (vdim + 2) * 4);
+    dim3 dgrid(n_seqs, kv_heads);
+#define MMA_ATTN(DD, DDV)                                                                                                \
+  do {                                                                                                                   \
+    if (tiles) {                                                                                                         \
+      if (msm > 48 * 1024)                                                                                               \
+        B200Q_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<DD, DDV>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                        (int)msm));                                                                      \
+      window_attn_mma_kernel<DD, DDV><<<mgrid, nw * 32, msm, st>>>(qs, (const bf16*)cache, block_table, bt_stride,       \
+                                                                   seq_desc, heads, kv_heads, block_size, window,        \
+                                                                   (const bf16*)gate, ld_gate, (bf16*)out, dec ? 1 : 0); \
+      B200Q_LAUNCH_CHECK();                                                                                              \
+    }                                                                                                                    \
+    if (dec) {                                                                                                           \
+      if (dsm > 48 * 1024)                                                                                               \
+        B200Q_CUDA(cudaFuncSetAttribute(window_attn_decode_mma_kernel<DD, DDV>,                                          \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm));                         \
+      window_attn_decode_mma_kernel<DD, DDV><<<dgrid, 128, dsm, st>>>(qs, (const bf16*)cache, block_table, bt_stride,    \
+                                                                      seq_desc, heads, kv_heads, block_size, window,     \
+                                                                      (const bf16*)gate, ld_gate, (bf16*)out);           \
+      B200Q_LAUNCH_CHECK();                                                                                              \
+    }                                                                                                                    \
+  } while (0)
+    if (dim == 64 && vdim == 64) MMA_ATTN(64, 64);
+    else if (dim == 64) MMA_ATTN(64, 128);
+    else if (vdim == 64) MMA_ATTN(128, 64);
+    else MMA_ATTN(128, 128);
+#undef MMA_ATTN
+    return B200Q_OK;
+  }
   dim3 grid(T_, kv_heads, (rep + 7) / 8);
   B200Q_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "window_attn: too many heads");
   const size_t smem = (size_t)(8 * dim + 32 * (dim + 1) + 32 * (vdim + 1)) * sizeof(float);
