@@ -696,7 +696,13 @@ def run_compare(args):
         cache rows the attention layers read, recurrent state read and written"""
         cache = state = 0
         for ly in spec.layers:
-            if ly.mixer == "latent_attention":
+            kind = getattr(ly, "kind", None)        # Paluzen's layer runs (a repeated layer counts once per pass)
+            if kind == "lightning":
+                state += B * ly.heads * ly.dim * ly.vdim * 4 * 2
+            elif kind == "parallel":
+                cache += B * min(C0 + 1, ly.window or C0 + 1) * ly.kv_heads * (ly.dim + ly.vdim) * 2
+                state += B * ly.r_heads * ly.r_dim * ly.r_dim * 4 * 2
+            elif ly.mixer == "latent_attention":
                 cache += B * min(C0, ly.window or C0) * (ly.kv_rank + ly.rot_dim) * 2
             elif ly.mixer == "general_delta":
                 state += B * ly.heads * ly.dim * ly.dim * 4 * 2
@@ -711,14 +717,16 @@ def run_compare(args):
     frac = lambda by, ms: round(by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3) if ms > 0 else None
     tf = lambda fl, ms: round(fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 3) if ms > 0 else None
     results = {}
-    if args.compare == "noridra":
-        # Noridra beside the closest existing design, Ramopel (layered, recurrent state slots, routed experts),
-        # at equal width, layer count and matrix bytes per token
-        for key in (args.compare_sizes or "noridra-1b,noridra-3b").split(","):
-            nspec, rspec = BUILTIN_SPECS[key], BUILTIN_SPECS[key.replace("noridra", "ramopel")]
+    if args.compare in ("noridra", "paluzen"):
+        # the design beside the closest existing one at equal width and layer count: Noridra beside Ramopel
+        # (layered, recurrent state slots, routed experts); Paluzen beside Noridra (windowed / chunked grouped-query
+        # attention on the tensor cores, decayed outer-product states, routed experts)
+        new, old = args.compare, {"noridra": "ramopel", "paluzen": "noridra"}[args.compare]
+        for key in (args.compare_sizes or f"{new}-1b,{new}-3b").split(","):
+            nspec, rspec = BUILTIN_SPECS[key], BUILTIN_SPECS[key.replace(new, old)]
             n, r = measure(nspec), measure(rspec)
             roof = {}
-            for name, spec, m in (("noridra", nspec, n), ("ramopel", rspec, r)):
+            for name, spec, m in ((new, nspec, n), (old, rspec, r)):
                 cache, state = decode_bytes(spec)
                 k = m["decode"]["kernel_ms_per_step"]
                 pf = 2.0 * (spec.weight_bytes_per_token() / 2 - spec.vocab * spec.width) * n_p * S_p
@@ -727,11 +735,11 @@ def run_compare(args):
                               "decode_recurrence_of_hbm": frac(state, k["prefill_attn"]),
                               "prefill_gemm_of_cublas": tf(pf, m["prefill"]["kernel_ms_per_run"]["gemm"]),
                               "decode_cache_mb": round(cache / 1e6, 2), "decode_state_mb": round(state / 1e6, 2)}
-            results[key] = {"noridra": n, "ramopel_equal_size": r,
-                            "matrix_gb_per_token": {"noridra": round(nspec.weight_bytes_per_token() / 1e9, 3),
-                                                    "ramopel": round(rspec.weight_bytes_per_token() / 1e9, 3)},
+            results[key] = {new: n, old + "_equal_size": r,
+                            "matrix_gb_per_token": {new: round(nspec.weight_bytes_per_token() / 1e9, 3),
+                                                    old: round(rspec.weight_bytes_per_token() / 1e9, 3)},
                             "roofline": roof}
-        print(json.dumps({"compare": "noridra", "dtype": "bf16", "data": "synthetic (random weights, random ids)",
+        print(json.dumps({"compare": new, "dtype": "bf16", "data": "synthetic (random weights, random ids)",
                           "peaks": peaks, "workload": {"prefill": f"{n_p} prompts x {S_p} tokens",
                                                        "decode": f"{B} sequences at context {C0}"},
                           "units": "decode_*_of_hbm: fraction of the measured HBM copy bandwidth (bytes a step must move / "
@@ -801,7 +809,7 @@ def main():
     ap.add_argument("--cpu-budget-s", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dry-run", action="store_true", help="host-logic self-test without a GPU (not a measurement)")
-    ap.add_argument("--compare", default=None, choices=["ramopel", "noridra"],
+    ap.add_argument("--compare", default=None, choices=["ramopel", "noridra", "paluzen"],
                     help="instead of the headline workload: prefill / decode throughput of this design beside the closest "
                          "existing model of equal size (ramopel: a Llama decoder; noridra: Ramopel), random weights, one "
                          "JSON line")

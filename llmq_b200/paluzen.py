@@ -390,6 +390,6 @@ def _cycle(width: int, vocab: int, n_layers: int, heads: int, kv_heads: int, dim
 
 # sizes that resemble a real model's layers (random weights; `random:<name>` as a model name)
 BUILTIN_SPECS = {
-    "paluzen-1b": _cycle(2048, 32768, 16, 16, 4, 128, 16, 4, 1024, "paluzen-1b"),
-    "paluzen-3b": _cycle(3072, 32768, 24, 24, 8, 128, 32, 6, 1536, "paluzen-3b"),
+    "paluzen-1b": _cycle(2048, 32768, 16, 16, 4, 128, 16, 4, 1536, "paluzen-1b"),
+    "paluzen-3b": _cycle(3072, 32768, 24, 24, 8, 128, 32, 6, 2304, "paluzen-3b"),
 }

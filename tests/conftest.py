@@ -8,6 +8,13 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+# the reference's own package (its unmodified BaseWorker, broker and CLI run in some host tests): from the
+# local install or the source tree, whichever exists; None where this checkout has neither
+REFERENCE = next((p for p in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference")
+                  if os.path.isdir(os.path.join(p, "llmq"))), None)
+needs_reference = pytest.mark.skipif(REFERENCE is None, reason="the reference llmq package is not available here")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu under gpurun)")
 

@@ -8,6 +8,8 @@ import os
 import subprocess
 import sys
 
+from tests.conftest import needs_reference
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ARGS = ["--dry-run", "--steps", "3", "--warmup", "2", "--jobs", "64", "--max-num-seqs", "256",
         "--max-num-batched-tokens", "256", "--max-model-len", "512", "--no-cpu-baseline"]
@@ -37,12 +39,14 @@ def _check(d, n):
     assert d["config"]["jobs_per_step_per_gpu"] == 64 and "workload" in d["config"]
 
 
+@needs_reference          # the end-to-end arm drives the reference's own BaseWorker
 def test_bench_host_logic_single_rank():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py")] + ARGS, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-3000:]
     _check(_line(r.stdout), 1)
 
 
+@needs_reference
 def test_bench_host_logic_two_ranks_gloo():
     port = 29600 + os.getpid() % 300
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",

@@ -67,6 +67,7 @@ def test_two_worker_processes_share_one_queue(tmp_path):
                 p.kill()
 
 
+@pytest.mark.skipif(REF is None, reason="reference llmq package not available")
 def test_queue_bench_tool_pipeline_mode_with_the_reference_dummy_worker(tmp_path):
     """tools/queue_bench.py (the process-level harness of BASELINE configs #3-#5) in its two-stage pipeline
     mode, with the reference's own DummyWorker processes standing in for the GPU workers: broker process,

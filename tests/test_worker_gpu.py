@@ -8,6 +8,8 @@ import sys
 
 import pytest
 
+from tests.conftest import needs_reference
+
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -19,6 +21,7 @@ for p in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
 os.environ.setdefault("LLMQ_LOG_LEVEL", "WARNING")
 
 
+@needs_reference
 def test_b200_worker_end_to_end_from_model_dir(cuda, tmp_path, monkeypatch):
     import aio_pika
     from llmq.core.broker import BrokerManager
@@ -97,6 +100,7 @@ def test_b200_worker_end_to_end_from_model_dir(cuda, tmp_path, monkeypatch):
     assert got["chat"].prompt == "Chat with 1 messages" and isinstance(got["chat"].result, str)
 
 
+@needs_reference
 def test_b200_worker_end_to_end_from_gemma2_model_dir(cuda, tmp_path, monkeypatch):
     """the same drop-in path with a Gemma-2 checkpoint directory (config.json says
     Gemma2ForCausalLM; tests/test_gemma2_host.py shows transformers loads the very same directory):
@@ -208,6 +212,7 @@ def test_two_engines_back_to_back_in_one_process_get_the_same_kv_pool(cuda):
     assert min(free_after) > free0 - (1 << 30), f"memory not returned to the driver: {free_after} vs {free0} before"
 
 
+@needs_reference
 def test_two_stage_pipeline_on_the_gpu_with_braces_in_stage1_output(cuda, tmp_path, monkeypatch):
     """config #4 with real model output: two B200Worker stages on the GPU, stage 1's
     text routed into stage 2's queue by the reference's unmodified `publish_pipeline_result`
