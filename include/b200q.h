@@ -369,24 +369,27 @@ int b200q_silu_glu(const void* gate_up_dev, void* y_dev, int64_t rows, int F, in
 
 /* plain RMS norm of fp32 rows, optionally followed by a token shift:
  *   n[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w;   y[t] = n[t] + (n[t-1] - n[t]) * shift       (shift NULL: y = n)
- * n[t-1] of a portion's first token is read from the sequence's state slot (zeros at position 0); the n of every
- * sequence's last token is left in carry [n_seqs, W] (b200q_store_carry moves it into the slot once every reader
- * of the old value has run).  rows != NULL (only without shift) gathers x[rows[i]] into output row i.
+ * n[t-1] of a portion's first token is read from the sequence's state slot (zeros at position 0).  The n of a
+ * sequence's last token replaces it: a portion of ONE token stores it in the slot itself (reader and writer are
+ * the same thread), a longer portion leaves it in carry [n_seqs, W], and b200q_store_carry (skip_single = 1) moves
+ * it into the slot once every reader of the old value has run — a step of single tokens needs no second launch.
+ * rows != NULL (only without shift) gathers x[rows[i]] into output row i.
  * y_t (model dtype) and / or y_f32 receive the result. */
 int b200q_rmsnorm_shift(const float* x_dev, const int32_t* rows_dev, const float* w_dev, const float* shift_dev,
-                        const float* state_dev, long long slot_stride, const int32_t* seq_desc_dev,
+                        float* state_dev, long long slot_stride, const int32_t* seq_desc_dev,
                         const int32_t* row_seq_dev, int n_seqs, float* carry_dev, void* y_t_dev, float* y_f32_dev,
                         int n, int W, float eps, int dtype, void* stream);
 /* state[slot of sequence s][0..W) <- src row of s: last_rows = 1: the last row of the sequence's portion in a
- * [T, W] buffer; 0: row s of a [n_seqs, W] buffer */
+ * [T, W] buffer; 0: row s of a [n_seqs, W] buffer.  skip_single = 1 leaves portions of one token alone. */
 int b200q_store_carry(const float* src_dev, int last_rows, float* state_dev, long long slot_stride,
-                      const int32_t* seq_desc_dev, int n_seqs, int W, void* stream);
+                      const int32_t* seq_desc_dev, int n_seqs, int W, int skip_single, void* stream);
 /* n_mix blends of every row with the previous token's row: out[t, s*W + c] = h[t,c] + (h[t-1,c] - h[t,c]) *
  * mu[s*W + c]; h fp32 [T, W]; h[t-1] of a portion's first token from the state slot (zeros at position 0);
- * out [T, n_mix*W] in the model dtype */
-int b200q_shift_blend(const float* h_dev, const float* mu_dev, int n_mix, const float* state_dev,
-                      long long slot_stride, const int32_t* seq_desc_dev, const int32_t* row_seq_dev, void* out_dev,
-                      int T, int W, int dtype, void* stream);
+ * out [T, n_mix*W] in the model dtype.  store_single = 1: a portion of one token also stores its row in the slot
+ * (the rows of longer portions are stored by b200q_store_carry with last_rows = 1, skip_single = 1) */
+int b200q_shift_blend(const float* h_dev, const float* mu_dev, int n_mix, float* state_dev,
+                      long long slot_stride, const int32_t* seq_desc_dev, const int32_t* row_seq_dev, int store_single,
+                      void* out_dev, int T, int W, int dtype, void* stream);
 /* z <- relu(z)^2 in place over n values */
 int b200q_relu2(void* z_dev, int64_t n, int dtype, void* stream);
 /* out = tanh(in) (fp32 in, model dtype out) */
@@ -437,6 +440,9 @@ int b200q_moe_route_grouped(const float* logits_dev, const float* correction_dev
 /* x += a_scale * a (+ b_scale * b, b may be NULL); a, b in the model dtype */
 int b200q_residual_add(float* x_dev, const void* a_dev, float a_scale, const void* b_dev, float b_scale, int T, int W,
                        int dtype, void* stream);
+/* x += a_scale * a (+ b_scale * b), then y = x / sqrt(mean(x^2) + eps) * w (model dtype) in the same pass */
+int b200q_residual_add_rmsnorm(float* x_dev, const void* a_dev, float a_scale, const void* b_dev, float b_scale,
+                               const float* w_dev, void* y_dev, int T, int W, float eps, int dtype, void* stream);
 /* x[t] += sum_k wts[t,k] * (idx[t,k] < n_real ? expert_out[pair_pos[t*top+k]] : h[t]) */
 int b200q_residual_add_routed(float* x_dev, const void* expert_out_dev, const int32_t* pair_pos_dev,
                               const int32_t* idx_dev, const float* wts_dev, int top, int n_real, const void* h_dev,

@@ -711,11 +711,13 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
     } else if (d.mixer == B200Q_MIXER_DECAY_MIX) {
       const int R = d.decay_rank, NQ = 4 * HD;
       TRY(EW, (double)T * W * (4 + 5 * es),
-          b200q_shift_blend(y->hf, l.mu, 5, y->state + l.prev_off, y->state_slot_floats, b->seq_desc, b->row_seq, y->blend,
-                            T, W, dt, stream));
-      // every reader of the carried input has run: the last row of each portion takes its place
-      TRY(EW, 8.0 * b->n_rows * W,
-          b200q_store_carry(y->hf, 1, y->state + l.prev_off, y->state_slot_floats, b->seq_desc, b->n_rows, W, stream));
+          b200q_shift_blend(y->hf, l.mu, 5, y->state + l.prev_off, y->state_slot_floats, b->seq_desc, b->row_seq, 1,
+                            y->blend, T, W, dt, stream));
+      // every reader of the carried input has run: the last row of each longer portion takes its place (single
+      // tokens stored theirs while blending, so a step of single tokens launches nothing here)
+      if (T > b->n_rows)
+        TRY(EW, 8.0 * b->n_rows * W,
+            b200q_store_carry(y->hf, 1, y->state + l.prev_off, y->state_slot_floats, b->seq_desc, b->n_rows, W, 1, stream));
       // r, k, v, gate: product g reads blend g (a column slice of the blend rows)
       TRY(B200Q_PROF_GEMM, 2.0 * T * 4.0 * HD * W,
           b200q_linear_batched(y->blend, 5 * W, W, l.proj, (long long)HD * W, y->proj, NQ, HD, T, HD, W, 4, dt, 0, stream));
@@ -874,18 +876,22 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
           b200q_rmsnorm_shift(y->x, nullptr, l.norm1, c.token_shift ? l.shift : nullptr, y->state + l.shift_off,
                               y->state_slot_floats, b->seq_desc, b->row_seq, b->n_rows, y->carry, y->h1,
                               want_f32 ? y->hf : nullptr, T, W, c.rms_eps, dt, stream));
-      if (c.token_shift)
+      if (c.token_shift && T > b->n_rows)
         TRY(EW, 8.0 * b->n_rows * W,
-            b200q_store_carry(y->carry, 0, y->state + l.shift_off, y->state_slot_floats, b->seq_desc, b->n_rows, W, stream));
+            b200q_store_carry(y->carry, 0, y->state + l.shift_off, y->state_slot_floats, b->seq_desc, b->n_rows, W, 1,
+                              stream));
       if ((rc = run_mixer(l))) return rc;
       if (side && (rc = run_sequence_mixer(l.side[0], y->mix2))) return rc;
-      TRY(EW, (double)T * W * (8 + (side ? 2 : 1) * es),
-          b200q_residual_add(y->x, y->mix, d.mix_scale != 0.f ? d.mix_scale : 1.f, side ? y->mix2 : nullptr,
-                             side && l.side[0].d.mix_scale != 0.f ? l.side[0].d.mix_scale : 1.f, T, W, dt, stream));
+      const float sa = d.mix_scale != 0.f ? d.mix_scale : 1.f;
+      const float sb = side && l.side[0].d.mix_scale != 0.f ? l.side[0].d.mix_scale : 1.f;
+      if (!has_ff)
+        TRY(EW, (double)T * W * (8 + (side ? 2 : 1) * es),
+            b200q_residual_add(y->x, y->mix, sa, side ? y->mix2 : nullptr, sb, T, W, dt, stream));
       if (has_ff) {
-        TRY(EW, (double)T * W * (4 + es),
-            b200q_rmsnorm_shift(y->x, nullptr, l.norm2, nullptr, nullptr, 0, nullptr, nullptr, 0, nullptr, y->h2, nullptr, T,
-                                W, c.rms_eps, dt, stream));
+        // the sum that closes the mixer and the norm that opens the feed-forward, one pass
+        TRY(EW, (double)T * W * (8 + (side ? 3 : 2) * es),
+            b200q_residual_add_rmsnorm(y->x, y->mix, sa, side ? y->mix2 : nullptr, sb, l.norm2, y->h2, T, W, c.rms_eps, dt,
+                                       stream));
         if (d.ff == B200Q_FF_RELU2) {
           const int F = d.ff_dim;
           LIN(y->h2, W, l.up, nullptr, y->ffh, F, F, W, 0);

@@ -28,8 +28,8 @@ __global__ void __launch_bounds__(256) rmsnorm_shift_kernel(const float* __restr
                                                             const float* __restrict__ state, long long slot_stride,
                                                             const int32_t* __restrict__ seq_desc,
                                                             const int32_t* __restrict__ row_seq, float* __restrict__ carry,
-                                                            T* __restrict__ y_t, float* __restrict__ y_f32, int W,
-                                                            float eps) {
+                                                            float* __restrict__ state_w, T* __restrict__ y_t,
+                                                            float* __restrict__ y_f32, int W, float eps) {
   __shared__ float red[32];
   const int i = blockIdx.x;
   const int t = rows ? rows[i] : i;
@@ -65,15 +65,45 @@ __global__ void __launch_bounds__(256) rmsnorm_shift_kernel(const float* __restr
     const float v = n + (p - n) * shift[c];
     if (y_t) stf(y_t + (long long)i * W + c, v);
     if (y_f32) y_f32[(long long)i * W + c] = v;
-    if (last) carry[(long long)s * W + c] = n;
+    // a portion of one token is read and written by this CTA alone (each thread its own channels): the row goes
+    // straight into the slot; longer portions leave it in `carry` until every reader of the old row has run
+    if (last) (first ? state_w + (long long)sq.slot * slot_stride : carry + (long long)s * W)[c] = n;
   }
+}
+
+// x <- x + sa * a (+ sb * b), then y = x / rms(x) * w: the sum that closes a mixer and the norm that opens the
+// feed-forward in one pass over the row (CTA per row; the row stays in registers between the two)
+constexpr int ADDNORM_MAX = 16;  // channels per thread: rows of up to 4096 values stay in registers
+template <typename T>
+__global__ void __launch_bounds__(256) residual_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ a, float sa,
+                                                                   const T* __restrict__ b, float sb,
+                                                                   const float* __restrict__ w, T* __restrict__ y, int W,
+                                                                   float eps) {
+  __shared__ float red[32];
+  const long long base = (long long)blockIdx.x * W;
+  const bool keep = W <= ADDNORM_MAX * (int)blockDim.x;
+  float v[ADDNORM_MAX];
+  float ss = 0.f;
+  int q = 0;
+  for (int c = threadIdx.x; c < W; c += blockDim.x, ++q) {
+    float t = sa * ldf(a + base + c);
+    if (b) t = fmaf(sb, ldf(b + base + c), t);
+    t += x[base + c];
+    x[base + c] = t;
+    if (keep) v[q < ADDNORM_MAX ? q : 0] = t;
+    ss = fmaf(t, t, ss);
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
+  q = 0;
+  for (int c = threadIdx.x; c < W; c += blockDim.x, ++q)
+    stf(y + base + c, (keep ? v[q < ADDNORM_MAX ? q : 0] : x[base + c]) * inv * w[c]);
 }
 
 __global__ void __launch_bounds__(256) store_carry_kernel(const float* __restrict__ src, int last_rows,
                                                           float* __restrict__ state, long long slot_stride,
-                                                          const int32_t* __restrict__ seq_desc, int W) {
+                                                          const int32_t* __restrict__ seq_desc, int W, int skip_single) {
   const SeqView sq = seq_view(seq_desc, blockIdx.x);
-  if (sq.n <= 0) return;
+  if (sq.n <= 0 || (skip_single && sq.n == 1)) return;  // single tokens were stored by their reader
   const float* r = src + (long long)(last_rows ? sq.row0 + sq.n - 1 : blockIdx.x) * W;
   float* d = state + (long long)sq.slot * slot_stride;
   for (int c = threadIdx.x; c < W; c += blockDim.x) d[c] = r[c];
@@ -83,15 +113,18 @@ template <typename T>
 __global__ void __launch_bounds__(256) shift_blend_kernel(const float* __restrict__ h, const float* __restrict__ mu,
                                                           int n_mix, const float* __restrict__ state,
                                                           long long slot_stride, const int32_t* __restrict__ seq_desc,
-                                                          const int32_t* __restrict__ row_seq, T* __restrict__ out, int W) {
+                                                          const int32_t* __restrict__ row_seq, float* __restrict__ state_w,
+                                                          T* __restrict__ out, int W) {
   const int t = blockIdx.x;
   const SeqView sq = seq_view(seq_desc, row_seq[t]);
   const float* hr = h + (long long)t * W;
   const float* pr = t > sq.row0 ? hr - W : (sq.pos0 > 0 ? state + (long long)sq.slot * slot_stride : nullptr);
+  float* keep = (state_w && sq.n == 1) ? state_w + (long long)sq.slot * slot_stride : nullptr;  // see rmsnorm_shift
   T* o = out + (long long)t * n_mix * W;
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
     const float v = hr[c], d = (pr ? pr[c] : 0.f) - v;
     for (int s = 0; s < n_mix; ++s) stf(o + (long long)s * W + c, fmaf(d, mu[(long long)s * W + c], v));
+    if (keep) keep[c] = v;
   }
 }
 
@@ -326,7 +359,7 @@ using namespace b200q;
 
 extern "C" {
 
-int b200q_rmsnorm_shift(const float* x, const int32_t* rows, const float* w, const float* shift, const float* state,
+int b200q_rmsnorm_shift(const float* x, const int32_t* rows, const float* w, const float* shift, float* state,
                         long long slot_stride, const int32_t* seq_desc, const int32_t* row_seq, int n_seqs, float* carry,
                         void* y_t, float* y_f32, int n, int W, float eps, int dtype, void* stream) {
   B200Q_CHECK_ARG(x && w && (y_t || y_f32) && n >= 0 && W > 0 && eps > 0.f && is_dtype(dtype),
@@ -335,28 +368,30 @@ int b200q_rmsnorm_shift(const float* x, const int32_t* rows, const float* w, con
                   "rmsnorm_shift: a shift needs the state, the per-sequence view and the carry buffer, and no row gather");
   if (n == 0) return B200Q_OK;
   DISPATCH_T(dtype, (rmsnorm_shift_kernel<T><<<n, 256, 0, as_stream(stream)>>>(x, rows, w, shift, state, slot_stride,
-                                                                               seq_desc, row_seq, carry, (T*)y_t, y_f32, W,
-                                                                               eps)));
+                                                                               seq_desc, row_seq, carry, state, (T*)y_t,
+                                                                               y_f32, W, eps)));
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
 
 int b200q_store_carry(const float* src, int last_rows, float* state, long long slot_stride, const int32_t* seq_desc,
-                      int n_seqs, int W, void* stream) {
+                      int n_seqs, int W, int skip_single, void* stream) {
   B200Q_CHECK_ARG(src && state && seq_desc && n_seqs >= 0 && W > 0, "store_carry: bad argument");
   if (n_seqs == 0) return B200Q_OK;
-  store_carry_kernel<<<n_seqs, 256, 0, as_stream(stream)>>>(src, last_rows, state, slot_stride, seq_desc, W);
+  store_carry_kernel<<<n_seqs, 256, 0, as_stream(stream)>>>(src, last_rows, state, slot_stride, seq_desc, W, skip_single);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
 
-int b200q_shift_blend(const float* h, const float* mu, int n_mix, const float* state, long long slot_stride,
-                      const int32_t* seq_desc, const int32_t* row_seq, void* out, int T_, int W, int dtype, void* stream) {
+int b200q_shift_blend(const float* h, const float* mu, int n_mix, float* state, long long slot_stride,
+                      const int32_t* seq_desc, const int32_t* row_seq, int store_single, void* out, int T_, int W, int dtype,
+                      void* stream) {
   B200Q_CHECK_ARG(h && mu && n_mix > 0 && state && seq_desc && row_seq && out && T_ >= 0 && W > 0 && is_dtype(dtype),
                   "shift_blend: bad argument");
   if (T_ == 0) return B200Q_OK;
   DISPATCH_T(dtype, (shift_blend_kernel<T><<<T_, 256, 0, as_stream(stream)>>>(h, mu, n_mix, state, slot_stride, seq_desc,
-                                                                              row_seq, (T*)out, W)));
+                                                                              row_seq, store_single ? state : nullptr,
+                                                                              (T*)out, W)));
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -430,6 +465,16 @@ int b200q_residual_add(float* x, const void* a, float a_scale, const void* b, fl
   const long long total = (long long)T_ * W;
   DISPATCH_T(dtype, (residual_add_kernel<T><<<grid_for(total), 256, 0, as_stream(stream)>>>(x, (const T*)a, a_scale,
                                                                                             (const T*)b, b_scale, total)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_residual_add_rmsnorm(float* x, const void* a, float a_scale, const void* b, float b_scale, const float* w,
+                               void* y, int T_, int W, float eps, int dtype, void* stream) {
+  B200Q_CHECK_ARG(x && a && w && y && T_ >= 0 && W > 0 && eps > 0.f && is_dtype(dtype), "residual_add_rmsnorm: bad argument");
+  if (T_ == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (residual_add_rmsnorm_kernel<T><<<T_, 256, 0, as_stream(stream)>>>(x, (const T*)a, a_scale, (const T*)b,
+                                                                                       b_scale, w, (T*)y, W, eps)));
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

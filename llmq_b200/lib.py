@@ -230,8 +230,9 @@ SIGNATURES = {
     "b200q_argmax_f32": (_i, [_vp, _vp, _i, _i, _vp]),
     # pre-norm layers, token shift, mixers 6-8
     "b200q_rmsnorm_shift": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
-    "b200q_store_carry": (_i, [_vp, _i, _vp, _ll, _vp, _i, _i, _vp]),
-    "b200q_shift_blend": (_i, [_vp, _vp, _i, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200q_store_carry": (_i, [_vp, _i, _vp, _ll, _vp, _i, _i, _i, _vp]),
+    "b200q_shift_blend": (_i, [_vp, _vp, _i, _vp, _ll, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "b200q_residual_add_rmsnorm": (_i, [_vp, _vp, _f, _vp, _f, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200q_relu2": (_i, [_vp, _i64, _i, _vp]),
     "b200q_tanh_cast": (_i, [_vp, _vp, _i64, _i, _vp]),
     "b200q_act_to_f32": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _i, _vp]),

@@ -286,7 +286,7 @@ def test_shifted_norm_carries_the_previous_row(cuda):
         L.check(lib.b200q_rmsnorm_shift(x.data_ptr(), None, wd.data_ptr(), sd.data_ptr(), state.data_ptr(), W + 4,
                                         desc.data_ptr(), row_seq.data_ptr(), len(parts), carry.data_ptr(), None,
                                         y.data_ptr(), rows, W, 1e-5, L.DTYPE_F32, None))
-        L.check(lib.b200q_store_carry(carry.data_ptr(), 0, state.data_ptr(), W + 4, desc.data_ptr(), len(parts), W, None))
+        L.check(lib.b200q_store_carry(carry.data_ptr(), 0, state.data_ptr(), W + 4, desc.data_ptr(), len(parts), W, 1, None))
         torch.cuda.synchronize()
         r0 = 0
         for s, n in parts:
