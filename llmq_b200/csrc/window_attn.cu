@@ -328,12 +328,13 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(const float* __res
 // ------------------------------------------------------------------------------------------------
 // The same for a single decoded token of a sequence: one CTA (4 warps) per (sequence, key/value head).  The M
 // rows of the tiles are the query heads of the group (<= 16), so one pass over the cached rows serves all of
-// them; warp w takes the 32-key tiles w, w+4, ... of the token's window through its own double-buffered
-// cp.async ring (no CTA barrier inside the loop) and keeps its own softmax state; the four states are merged
-// through shared memory in a fixed order at the end.
+// them; warp w takes the key tiles w, w+4, ... (16 or 32 cached rows each) of the token's window through its own
+// double-buffered cp.async ring (no CTA barrier inside the loop) and keeps its own softmax state; the four states
+// are merged through shared memory in a fixed order at the end.  The tile size is chosen so that three CTAs fit
+// an SM: the kernel lives on loads in flight, not on arithmetic.
 // ------------------------------------------------------------------------------------------------
-constexpr int WDEC_KEYS = 32, WDEC_WARPS = 4;
-template <int D, int DV>
+constexpr int WDEC_WARPS = 4;
+template <int D, int DV, int WDEC_KEYS>
 __global__ void __launch_bounds__(128) window_attn_decode_mma_kernel(const float* __restrict__ qs,
                                                                      const bf16* __restrict__ cache,
                                                                      const int32_t* __restrict__ block_table,
@@ -398,15 +399,16 @@ __global__ void __launch_bounds__(128) window_attn_decode_mma_kernel(const float
     if (c + WDEC_WARPS < ntiles) load_tile(c + WDEC_WARPS, buf ^ 1);
     const bf16* kb = kw + (long long)buf * WDEC_KEYS * (LDK + LDV);
     const uint32_t kb_s = smem_u32(kb), vb_s = smem_u32(kb + WDEC_KEYS * LDK);
-    float s[4][4];
+    constexpr int NT = WDEC_KEYS / 8;  // 8-key score tiles of a key tile
+    float s[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       uint32_t a0, a1, a2, a3;
       ldsm_x4(q_s + a_off + ks * 32, a0, a1, a2, a3);
 #pragma unroll
-      for (int nt2 = 0; nt2 < 2; ++nt2) {
+      for (int nt2 = 0; nt2 < NT / 2; ++nt2) {
         uint32_t b0, b1, b2, b3;
         ldsm_x4(kb_s + kq_off + (uint32_t)(nt2 * 16 * LDK * 2 + ks * 32), b0, b1, b2, b3);
         mma_bf16_16816(s[2 * nt2], a0, a1, a2, a3, b0, b1);
@@ -415,7 +417,7 @@ __global__ void __launch_bounds__(128) window_attn_decode_mma_kernel(const float
     }
     float rmax[2] = {WATT_NEG, WATT_NEG};
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int j = j0 + nt * 8 + 2 * q4 + (e & 1), r = e >> 1;
@@ -434,7 +436,7 @@ __global__ void __launch_bounds__(128) window_attn_decode_mma_kernel(const float
     }
     float psum[2] = {0.f, 0.f};
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float pv = round_bf16(__expf(s[nt][e] - m_[e >> 1]));
@@ -538,6 +540,17 @@ static int window_attn_mma_mode() {  // B200Q_WINDOW_ATTN_MMA=0: the scalar kern
   return mode;
 }
 
+// cached rows per tile of the decode kernel: 32, or 16 where 32 would leave room for one CTA per SM only
+// (B200Q_WINDOW_DECODE_KEYS = 16 / 32 overrides)
+static int window_attn_decode_keys(int dim, int vdim) {
+  static const int forced = [] {
+    const char* v = getenv("B200Q_WINDOW_DECODE_KEYS");
+    return v ? atoi(v) : 0;
+  }();
+  if (forced == 16 || forced == 32) return forced;
+  return dim + vdim > 128 ? 16 : 32;
+}
+
 int b200q_window_attn(const float* qs, const void* cache, const int32_t* block_table, int bt_stride, const int32_t* row_seq,
                       const int32_t* positions, const int32_t* seq_desc, int n_seqs, int T_, int heads, int kv_heads,
                       int dim, int vdim, int block_size, int window, const void* gate, int ld_gate, void* out, int dtype,
@@ -561,7 +574,8 @@ int b200q_window_attn(const float* qs, const void* cache, const int32_t* block_t
     // single decoded tokens go to the kernel whose rows are the heads of a group (groups of up to 16 heads); a
     // step of single tokens only (T == n_seqs) needs no tile kernel
     const bool dec = rep <= 16, tiles = !dec || T_ > n_seqs;
-    const size_t dsm = std::max((size_t)16 * (dim + 8) * 2 + (size_t)WDEC_WARPS * 2 * WDEC_KEYS * (dim + vdim + 16) * 2,
+    const int dkeys = window_attn_decode_keys(dim, vdim);
+    const size_t dsm = std::max((size_t)16 * (dim + 8) * 2 + (size_t)WDEC_WARPS * 2 * dkeys * (dim + vdim + 16) * 2,
                                 (size_t)16 * (dim + 8) * 2 + (size_t)WDEC_WARPS * 16 * (vdim + 2) * 4);
     dim3 dgrid(n_seqs, kv_heads);
 #define MMA_ATTN(DD, DDV)                                                                                                \
@@ -576,12 +590,11 @@ int b200q_window_attn(const float* qs, const void* cache, const int32_t* block_t
       B200Q_LAUNCH_CHECK();                                                                                              \
     }                                                                                                                    \
     if (dec) {                                                                                                           \
+      auto dk = dkeys == 16 ? window_attn_decode_mma_kernel<DD, DDV, 16> : window_attn_decode_mma_kernel<DD, DDV, 32>;   \
       if (dsm > 48 * 1024)                                                                                               \
-        B200Q_CUDA(cudaFuncSetAttribute(window_attn_decode_mma_kernel<DD, DDV>,                                          \
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm));                         \
-      window_attn_decode_mma_kernel<DD, DDV><<<dgrid, 128, dsm, st>>>(qs, (const bf16*)cache, block_table, bt_stride,    \
-                                                                      seq_desc, heads, kv_heads, block_size, window,     \
-                                                                      (const bf16*)gate, ld_gate, (bf16*)out);           \
+        B200Q_CUDA(cudaFuncSetAttribute(dk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm));                     \
+      dk<<<dgrid, 128, dsm, st>>>(qs, (const bf16*)cache, block_table, bt_stride, seq_desc, heads, kv_heads, block_size, \
+                                  window, (const bf16*)gate, ld_gate, (bf16*)out);                                       \
       B200Q_LAUNCH_CHECK();                                                                                              \
     }                                                                                                                    \
   } while (0)
