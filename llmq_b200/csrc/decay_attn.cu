@@ -4,9 +4,9 @@
 //   decay per token and key channel:  o = (S + diag(bonus) k v^T)^T q;   S <- diag(w) S + k v^T  (reads the old one)
 // followed by a norm over groups of the output row, a weight and a gate (gated_rmsnorm_kernel).
 //
-// One warp per (sequence, head, 8 value columns): columns of the state are independent, so a head spreads
-// over vdim/8 CTAs; four lanes share a column, each with a quarter of it (dim/4 values, zero-padded) in
-// registers, partial dot products summed by two butterfly shuffles.  q, k (and w) of 8 tokens at a time arrive
+// One warp per (sequence, head, 8 or 16 value columns): columns of the state are independent, so a head spreads
+// over many CTAs; four lanes share a column, each with a quarter of it (zero-padded) in
+// registers, partial dot products summed by butterfly shuffles.  q, k (and w) of 8 tokens at a time arrive
 // in shared memory by cp.async one group ahead, v of the group is prefetched into registers.  The order of
 // every sum is fixed, so a token's output does not depend on how the prompt was cut.
 #include <stdlib.h>
@@ -25,72 +25,104 @@ __device__ __forceinline__ SeqView seq_view(const int32_t* __restrict__ seq_desc
   return {v.x, v.y, v.z, v.w};
 }
 
-constexpr int DATT_G = 8, DATT_COLS = 8;
+constexpr int DATT_G = 8;  // tokens staged per group
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
 
-// VECW: decay per token and key channel (with the bonus); else one constant per head
-template <int DT, bool VECW>
+// VECW: decay per token and key channel (with the bonus); else one constant per head.  NC: value columns per lane
+// group (the warp covers 8 * NC columns): with two, every k / q / w vector read from shared memory serves twice
+// as many multiply-adds and each lane carries two independent chains.
+// LPC: lanes that share a column (the warp covers 32 / LPC * NC columns).
+template <int DT, bool VECW, int NC, int LPC>
 __global__ void __launch_bounds__(32) decay_attn_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off,
                                                         int v_off, const float* __restrict__ head_decay,
                                                         const float* __restrict__ w, int ldw,
                                                         const float* __restrict__ bonus, float* __restrict__ state,
                                                         long long slot_stride, const int32_t* __restrict__ seq_desc,
                                                         int heads, int dim, int vdim, float* __restrict__ raw) {
-  constexpr int QL = DT / 4;           // state values per lane
+  constexpr int QL = DT / LPC;         // state values per lane and column
+  constexpr int CW = 32 / LPC;         // columns of a warp per NC
   constexpr int NV = VECW ? 3 : 2;     // vectors per token in shared memory: k, q (, w)
   extern __shared__ __align__(16) float sm[];  // [2][G][NV*DT]
   const SeqView s = seq_view(seq_desc, blockIdx.x);
   if (s.n <= 0) return;
-  const int h = blockIdx.y, lane = threadIdx.x, sub = lane >> 3, j = blockIdx.z * DATT_COLS + (lane & 7);
+  const int h = blockIdx.y, lane = threadIdx.x, sub = lane / CW, j0 = blockIdx.z * (CW * NC) + lane % CW;
   const int q0 = sub * QL, HV = heads * vdim;
-  const bool on = j < vdim;
+  bool on[NC];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) on[c] = j0 + CW * c < vdim;
   const bool vec = (dim & 3) == 0 && (ldq & 3) == 0 && (q_off & 3) == 0 && (k_off & 3) == 0 &&
                    (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
                    (!VECW || ((ldw & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0));
   float* st = state + (long long)s.slot * slot_stride + (long long)h * dim * vdim;
   for (int e = lane; e < 2 * DATT_G * NV * DT; e += 32) sm[e] = 0.f;  // the padding stays zero
   __syncwarp();
+  const float* krow = qkv + k_off + h * dim;
+  const float* qrow = qkv + q_off + h * dim;
+  const float* wrow = VECW ? w + h * dim : nullptr;
+  // the 16-byte pieces of a token's vectors that this lane copies are the same for every token: where each comes
+  // from and where it lands is worked out once, so that a group's copies cost no index arithmetic
+  constexpr int NP = (NV * DT / 4 + 31) / 32;
+  const float* psrc[NP];
+  long long pld[NP];
+  int pdst[NP];
+  {
+    const int pv = dim / 4, per = NV * pv;
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+      const int pc = lane + 32 * i, which = pc / max(pv, 1), off = (pc - which * pv) * 4;
+      const bool live = vec && pc < per;
+      psrc[i] = !live ? nullptr : (which == 0 ? krow : which == 1 ? qrow : wrow) + off;
+      pld[i] = which == 2 ? ldw : ldq;
+      pdst[i] = which * DT + off;
+    }
+  }
   auto fetch = [&](int g0, int buf) {
     const int cnt = min(DATT_G, s.n - g0);
     float* dst0 = sm + (long long)buf * DATT_G * NV * DT;
     if (vec) {
-      const int pv = dim / 4, per = NV * pv;  // 16-byte pieces of one token
-      for (int e = lane; e < cnt * per; e += 32) {
-        const int tk = e / per, pc = e % per, which = pc / pv, off = (pc % pv) * 4;
-        const long long row = s.row0 + g0 + tk;
-        const float* src = which == 0   ? qkv + row * ldq + k_off + h * dim
-                           : which == 1 ? qkv + row * ldq + q_off + h * dim
-                                        : w + row * ldw + h * dim;
-        cp_async16(dst0 + tk * NV * DT + which * DT + off, src + off);
+      const long long row = s.row0 + g0;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        if (!psrc[i]) continue;
+        const float* src = psrc[i] + row * pld[i];
+        float* dst = dst0 + pdst[i];
+        for (int tk = 0; tk < cnt; ++tk, src += pld[i], dst += NV * DT) cp_async16(dst, src);
       }
     } else {
       for (int e = lane; e < cnt * NV * dim; e += 32) {
         const int tk = e / (NV * dim), i = e % (NV * dim), which = i / dim, d = i % dim;
         const long long row = s.row0 + g0 + tk;
-        dst0[tk * NV * DT + which * DT + d] = which == 0   ? qkv[row * ldq + k_off + h * dim + d]
-                                              : which == 1 ? qkv[row * ldq + q_off + h * dim + d]
-                                                           : w[row * ldw + h * dim + d];
+        dst0[tk * NV * DT + which * DT + d] =
+            which == 0 ? krow[row * ldq + d] : which == 1 ? qrow[row * ldq + d] : wrow[row * ldw + d];
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   fetch(0, 0);
-  float S[QL], U[VECW ? QL : 1];
+  float S[NC][QL], U[VECW ? QL : 1];
 #pragma unroll
-  for (int q = 0; q < QL; ++q) S[q] = (on && q0 + q < dim && s.pos0 > 0) ? st[(long long)(q0 + q) * vdim + j] : 0.f;
+  for (int c = 0; c < NC; ++c)
+#pragma unroll
+    for (int q = 0; q < QL; ++q)
+      S[c][q] = (on[c] && q0 + q < dim && s.pos0 > 0) ? st[(long long)(q0 + q) * vdim + j0 + CW * c] : 0.f;
   if (VECW) {
 #pragma unroll
     for (int q = 0; q < QL; ++q) U[q] = q0 + q < dim ? bonus[h * dim + q0 + q] : 0.f;
   }
   const float lam = VECW ? 1.f : head_decay[h];
+  const float* vcol = qkv + v_off + h * vdim + j0;
+  float* rcol = raw + h * vdim + j0;
   for (int g0 = 0, buf = 0; g0 < s.n; g0 += DATT_G, buf ^= 1) {
     const int cnt = min(DATT_G, s.n - g0);
-    float vj[DATT_G];
+    float vj[NC][DATT_G];
+    const float* vrow = vcol + (long long)(s.row0 + g0) * ldq;
+    float* rrow = rcol + (long long)(s.row0 + g0) * HV;
 #pragma unroll
-    for (int tk = 0; tk < DATT_G; ++tk)
-      vj[tk] = (on && tk < cnt) ? qkv[(long long)(s.row0 + g0 + tk) * ldq + v_off + h * vdim + j] : 0.f;
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+      for (int tk = 0; tk < DATT_G; ++tk) vj[c][tk] = (on[c] && tk < cnt) ? vrow[(long long)tk * ldq + CW * c] : 0.f;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();  // this group has landed; the other buffer is no longer read
     if (g0 + DATT_G < s.n) fetch(g0 + DATT_G, buf ^ 1);
@@ -101,45 +133,57 @@ __global__ void __launch_bounds__(32) decay_attn_kernel(const float* __restrict_
         const float4* k4 = reinterpret_cast<const float4*>(base + tk * NV * DT);
         const float4* q4 = reinterpret_cast<const float4*>(base + tk * NV * DT + DT);
         const float4* w4 = reinterpret_cast<const float4*>(base + tk * NV * DT + (VECW ? 2 * DT : 0));
-        const float v = vj[tk];
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+        float o[NC][4];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) o[c][0] = o[c][1] = o[c][2] = o[c][3] = 0.f;
 #pragma unroll
         for (int q = 0; q < QL / 4; ++q) {
           const float4 k = k4[q], qq = q4[q];
-          if (VECW) {
-            const float4 ww = w4[q];
-            const float a0 = k.x * v, a1 = k.y * v, a2 = k.z * v, a3 = k.w * v;
-            o0 = fmaf(fmaf(U[4 * q], a0, S[4 * q]), qq.x, o0);
-            o1 = fmaf(fmaf(U[4 * q + 1], a1, S[4 * q + 1]), qq.y, o1);
-            o2 = fmaf(fmaf(U[4 * q + 2], a2, S[4 * q + 2]), qq.z, o2);
-            o3 = fmaf(fmaf(U[4 * q + 3], a3, S[4 * q + 3]), qq.w, o3);
-            S[4 * q] = fmaf(ww.x, S[4 * q], a0);
-            S[4 * q + 1] = fmaf(ww.y, S[4 * q + 1], a1);
-            S[4 * q + 2] = fmaf(ww.z, S[4 * q + 2], a2);
-            S[4 * q + 3] = fmaf(ww.w, S[4 * q + 3], a3);
-          } else {
-            S[4 * q] = fmaf(lam, S[4 * q], k.x * v);
-            S[4 * q + 1] = fmaf(lam, S[4 * q + 1], k.y * v);
-            S[4 * q + 2] = fmaf(lam, S[4 * q + 2], k.z * v);
-            S[4 * q + 3] = fmaf(lam, S[4 * q + 3], k.w * v);
-            o0 = fmaf(S[4 * q], qq.x, o0);
-            o1 = fmaf(S[4 * q + 1], qq.y, o1);
-            o2 = fmaf(S[4 * q + 2], qq.z, o2);
-            o3 = fmaf(S[4 * q + 3], qq.w, o3);
+          float4 ww;
+          if (VECW) ww = w4[q];
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            const float v = vj[c][tk];
+            float* Sc = S[c] + 4 * q;
+            if (VECW) {
+              const float a0 = k.x * v, a1 = k.y * v, a2 = k.z * v, a3 = k.w * v;
+              o[c][0] = fmaf(fmaf(U[4 * q], a0, Sc[0]), qq.x, o[c][0]);
+              o[c][1] = fmaf(fmaf(U[4 * q + 1], a1, Sc[1]), qq.y, o[c][1]);
+              o[c][2] = fmaf(fmaf(U[4 * q + 2], a2, Sc[2]), qq.z, o[c][2]);
+              o[c][3] = fmaf(fmaf(U[4 * q + 3], a3, Sc[3]), qq.w, o[c][3]);
+              Sc[0] = fmaf(ww.x, Sc[0], a0);
+              Sc[1] = fmaf(ww.y, Sc[1], a1);
+              Sc[2] = fmaf(ww.z, Sc[2], a2);
+              Sc[3] = fmaf(ww.w, Sc[3], a3);
+            } else {
+              Sc[0] = fmaf(lam, Sc[0], k.x * v);
+              Sc[1] = fmaf(lam, Sc[1], k.y * v);
+              Sc[2] = fmaf(lam, Sc[2], k.z * v);
+              Sc[3] = fmaf(lam, Sc[3], k.w * v);
+              o[c][0] = fmaf(Sc[0], qq.x, o[c][0]);
+              o[c][1] = fmaf(Sc[1], qq.y, o[c][1]);
+              o[c][2] = fmaf(Sc[2], qq.z, o[c][2]);
+              o[c][3] = fmaf(Sc[3], qq.w, o[c][3]);
+            }
           }
         }
-        float o = (o0 + o1) + (o2 + o3);
-        o += __shfl_xor_sync(0xffffffffu, o, 8);
-        o += __shfl_xor_sync(0xffffffffu, o, 16);
-        if (on && sub == 0) raw[(long long)(s.row0 + g0 + tk) * HV + h * vdim + j] = o;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          float t = (o[c][0] + o[c][1]) + (o[c][2] + o[c][3]);
+#pragma unroll
+          for (int off = CW; off < 32; off <<= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+          if (on[c] && sub == 0) rrow[(long long)tk * HV + CW * c] = t;
+        }
       }
     }
   }
-  if (on) {
 #pragma unroll
-    for (int q = 0; q < QL; ++q)
-      if (q0 + q < dim) st[(long long)(q0 + q) * vdim + j] = S[q];
-  }
+  for (int c = 0; c < NC; ++c)
+    if (on[c]) {
+#pragma unroll
+      for (int q = 0; q < QL; ++q)
+        if (q0 + q < dim) st[(long long)(q0 + q) * vdim + j0 + CW * c] = S[c][q];
+    }
 }
 
 // out = raw / rms(group) * w * act(gate): CTA per (token, group of `group` consecutive values)
@@ -177,21 +221,39 @@ int b200q_decay_attn(const float* qkv, int ldq, int q_off, int k_off, int v_off,
                   "decay_attn: give either a decay per head, or a decay per token and channel with its bonus");
   if (n_seqs == 0) return B200Q_OK;
   cudaStream_t st = as_stream(stream);
-  dim3 grid(n_seqs, heads, (vdim + DATT_COLS - 1) / DATT_COLS);
+  // Many (sequence, head) pairs (decode) take two value columns per lane group while the state fits the registers
+  // (key sizes up to 64); few pairs (prompts) keep one, which gives twice the warps.  A column's sums have the
+  // same order in both, so the choice changes no result.  (Eight lanes per column were tried for prompt steps:
+  // no gain, a warp's time per token is its dependent instruction chain, not its multiply-adds.)
+  static const int forced = [] {  // B200Q_DECAY_ATTN_SPLIT = 1 (one column per lane group) / 2 (two columns)
+    const char* v = getenv("B200Q_DECAY_ATTN_SPLIT");
+    return v ? atoi(v) : 0;
+  }();
+  const long long pairs = (long long)n_seqs * heads;
+  bool two = dim <= 64 && vdim >= 16 && pairs * ((vdim + 15) / 16) >= 2 * 148;
+  if (forced == 1 || forced == 2) two = forced == 2 && dim <= 64;
+  const int cols = two ? 16 : 8;
+  dim3 grid(n_seqs, heads, (vdim + cols - 1) / cols);
   B200Q_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "decay_attn: too many heads or value columns");
-#define RECUR(DT)                                                                                                        \
+#define RECUR_(DT, NC)                                                                                                    \
   do {                                                                                                                   \
     if (w)                                                                                                               \
-      decay_attn_kernel<DT, true><<<grid, 32, (size_t)2 * DATT_G * 3 * DT * sizeof(float), st>>>(                        \
+      decay_attn_kernel<DT, true, NC, 4><<<grid, 32, (size_t)2 * DATT_G * 3 * DT * sizeof(float), st>>>(                 \
           qkv, ldq, q_off, k_off, v_off, head_decay, w, ldw, bonus, state, slot_stride, seq_desc, heads, dim, vdim, raw); \
     else                                                                                                                 \
-      decay_attn_kernel<DT, false><<<grid, 32, (size_t)2 * DATT_G * 2 * DT * sizeof(float), st>>>(                       \
+      decay_attn_kernel<DT, false, NC, 4><<<grid, 32, (size_t)2 * DATT_G * 2 * DT * sizeof(float), st>>>(                \
           qkv, ldq, q_off, k_off, v_off, head_decay, w, ldw, bonus, state, slot_stride, seq_desc, heads, dim, vdim, raw); \
+  } while (0)
+#define RECUR(DT)            \
+  do {                       \
+    if (two) RECUR_(DT, 2);  \
+    else RECUR_(DT, 1);      \
   } while (0)
   if (dim <= 32) RECUR(32);
   else if (dim <= 64) RECUR(64);
-  else if (dim <= 128) RECUR(128);
-  else RECUR(256);
+  else if (dim <= 128) RECUR_(128, 1);
+  else RECUR_(256, 1);
+#undef RECUR_
 #undef RECUR
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
