@@ -374,8 +374,7 @@ def _cycle(width: int, vocab: int, n_layers: int, heads: int, kv_heads: int, dim
     lh = width // 128
     layers: List[PaluzenLayer] = []
     for i in range(n_layers):
-        moe = dict(ff="moe", ff_dim=ff, n_experts=experts, n_identity=experts // 8, top_k=top,
-                   n_groups=max(1, (experts + experts // 8) // 9), keep_groups=max(1, (experts + experts // 8) // 18))
+        moe = dict(ff="moe", ff_dim=ff, n_experts=experts, n_identity=experts // 4, top_k=top, n_groups=4, keep_groups=2)
         if i == 0:
             moe = dict(ff="dense", ff_dim=4 * width)
         if i % 4 in (0, 3):
@@ -385,7 +384,7 @@ def _cycle(width: int, vocab: int, n_layers: int, heads: int, kv_heads: int, dim
             layers.append(PaluzenLayer(kind="parallel", heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, window=2048,
                                        rot_dims=dim // 2, scale=dim ** -0.5, left_scale=1.0, r_heads=width // 64, r_dim=64,
                                        r_rank=64, right_scale=1.0, **moe))
-    return PaluzenSpec(width=width, vocab=vocab, base_layers=layers, loop=loop, rms_eps=1e-5, logit_softcap=30.0, name=name)
+    return PaluzenSpec(width=width, vocab=vocab, base_layers=layers, loop=loop, rms_eps=1e-5, logit_softcap=50.0, name=name)
 
 
 # sizes that resemble a real model's layers (random weights; `random:<name>` as a model name)

@@ -179,9 +179,10 @@ WINDOW_CASES = [
     # (T, H, G, D, V, window, marked keys)
     (150, 4, 2, 24, 40, 21, [0, 20, 21, 47, 63, 64, 100]),        # window edges off pages and tiles
     (200, 2, 1, 64, 64, 64, [0, 15, 16, 63, 64, 127, 128, 135]),   # a window of one tile, pages at its edges
-    (300, 8, 2, 128, 128, 96, [3, 95, 96, 99, 191, 192, 200]),     # head size 128, window 96
+    (300, 4, 2, 128, 128, 80, [3, 79, 80, 83, 159, 160, 200]),     # head size 128, window 80
     (260, 3, 3, 16, 8, 0, [5]),                                    # every earlier key: one far back among hundreds
     (90, 16, 1, 64, 128, 17, [0, 16, 17, 33, 50]),                 # sixteen heads on one key head, values wider than keys
+    (70, 24, 1, 128, 64, 19, [0, 18, 19, 40]),                     # more heads per key head than a decode tile has rows
 ]
 
 
