@@ -165,6 +165,30 @@ __global__ void __launch_bounds__(256) act_to_f32_kernel(const T* __restrict__ i
   }
 }
 
+// bf16 rows, 8 values per thread (16-byte load, two 16-byte stores); C, both strides and both bases aligned
+__global__ void __launch_bounds__(256) act_to_f32_v8_kernel(const bf16* __restrict__ in, int ld_in, float* __restrict__ out,
+                                                            int ld_out, int C8, int act, long long total8) {
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total8; e += (long long)gridDim.x * blockDim.x) {
+    const long long t = e / C8;
+    const int c = (int)(e - t * C8) * 8;
+    const uint4 v = ld_v4(in + t * ld_in + c);
+    const uint32_t p[4] = {v.x, v.y, v.z, v.w};
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = bf16_lo(p[i]);
+      f[2 * i + 1] = bf16_hi(p[i]);
+    }
+    if (act == 1) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = siluf_(f[i]);
+    }
+    float4* o = reinterpret_cast<float4*>(out + t * ld_out + c);
+    o[0] = make_float4(f[0], f[1], f[2], f[3]);
+    o[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+}
+
 // a decay acts at every later token of its sequence: the fp32 model takes both exponentials through fp64
 template <bool EXACT>
 __global__ void __launch_bounds__(256) decay_from_logits_kernel(float* __restrict__ w, int ldw,
@@ -337,6 +361,37 @@ __global__ void __launch_bounds__(256) residual_add_routed_kernel(float* __restr
   }
 }
 
+// bf16 rows, 8 channels per thread: the token's chosen rows are read with 16-byte loads
+__global__ void __launch_bounds__(256) residual_add_routed_v8_kernel(float* __restrict__ x, const bf16* __restrict__ eout,
+                                                                     const int32_t* __restrict__ pair_pos,
+                                                                     const int32_t* __restrict__ idx,
+                                                                     const float* __restrict__ wts, int top, int n_real,
+                                                                     const bf16* __restrict__ h, int Tn, int W8) {
+  const long long total = (long long)Tn * W8;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(e / W8), c = (int)(e - (long long)t * W8) * 8;
+    const long long at = (long long)t * W8 * 8 + c;
+    float ff[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top; ++k) {
+      const long long p = (long long)t * top + k;
+      const uint4 v = idx[p] < n_real ? ld_v4(eout + (long long)pair_pos[p] * W8 * 8 + c) : ld_v4(h + at);
+      const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+      const float wk = wts[p];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ff[2 * i] = fmaf(wk, bf16_lo(q[i]), ff[2 * i]);
+        ff[2 * i + 1] = fmaf(wk, bf16_hi(q[i]), ff[2 * i + 1]);
+      }
+    }
+    float4* xo = reinterpret_cast<float4*>(x + at);
+    float4 a = xo[0], b = xo[1];
+    a.x += ff[0]; a.y += ff[1]; a.z += ff[2]; a.w += ff[3];
+    b.x += ff[4]; b.y += ff[5]; b.z += ff[6]; b.w += ff[7];
+    xo[0] = a;
+    xo[1] = b;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                           T* __restrict__ out, int Tn, int W) {
@@ -420,8 +475,13 @@ int b200q_act_to_f32(const void* in, int ld_in, float* out, int ld_out, int C, i
                   "act_to_f32: bad argument");
   if (T_ == 0) return B200Q_OK;
   const long long total = (long long)T_ * C;
-  DISPATCH_T(dtype, (act_to_f32_kernel<T><<<grid_for(total), 256, 0, as_stream(stream)>>>((const T*)in, ld_in, out, ld_out,
-                                                                                          C, act, total)));
+  if (dtype == B200Q_DTYPE_BF16 && C % 8 == 0 && ld_in % 8 == 0 && ld_out % 4 == 0 &&
+      ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0)
+    act_to_f32_v8_kernel<<<grid_for(total / 8), 256, 0, as_stream(stream)>>>((const bf16*)in, ld_in, out, ld_out, C / 8, act,
+                                                                             total / 8);
+  else
+    DISPATCH_T(dtype, (act_to_f32_kernel<T><<<grid_for(total), 256, 0, as_stream(stream)>>>((const T*)in, ld_in, out,
+                                                                                            ld_out, C, act, total)));
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -486,8 +546,13 @@ int b200q_residual_add_routed(float* x, const void* expert_out, const int32_t* p
                       is_dtype(dtype),
                   "residual_add_routed: bad argument");
   if (T_ == 0) return B200Q_OK;
-  DISPATCH_T(dtype, (residual_add_routed_kernel<T><<<grid_for((long long)T_ * W), 256, 0, as_stream(stream)>>>(
-                        x, (const T*)expert_out, pair_pos, idx, wts, top, n_real, (const T*)h, T_, W)));
+  if (dtype == B200Q_DTYPE_BF16 && W % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(expert_out) | reinterpret_cast<uintptr_t>(h)) & 15) == 0)
+    residual_add_routed_v8_kernel<<<grid_for((long long)T_ * W / 8), 256, 0, as_stream(stream)>>>(
+        x, (const bf16*)expert_out, pair_pos, idx, wts, top, n_real, (const bf16*)h, T_, W / 8);
+  else
+    DISPATCH_T(dtype, (residual_add_routed_kernel<T><<<grid_for((long long)T_ * W), 256, 0, as_stream(stream)>>>(
+                          x, (const T*)expert_out, pair_pos, idx, wts, top, n_real, (const T*)h, T_, W)));
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
