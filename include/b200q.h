@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200Q_VERSION 4
+#define B200Q_VERSION 5
 
 #define B200Q_OK 0
 #define B200Q_EINVAL (-1)   /* bad argument / unsupported shape            */
@@ -455,6 +455,64 @@ int b200q_argmax_f32(const float* logits_dev, int32_t* ids_dev, int B, int V, vo
 int b200q_f32_to_bf16(const float* in_dev, void* out_dev, int64_t n, void* stream);
 int b200q_copy_f32(const float* in_dev, float* out_dev, int64_t n, void* stream);
 
+/* ---- sandwich layers and the options of window / latent attention (sandwich_ops.cu) ----------------------------- */
+
+/* rotation frequencies as b200q_layer_desc describes them (host only): freq_out fp64 [rot_dims/2], *mag_out the
+ * factor of sine and cosine */
+int b200q_rot_frequencies(int rot_dims, double base, double factor, double original, double fast, double slow,
+                          double* freq_out, float* mag_out);
+/* y[i] = norm(x[rows ? rows[i] : i]) in the model dtype; kind B200Q_NORM_DYT (w = [w | b | alpha]), B200Q_NORM_RMS
+ * (w = [w]) or B200Q_NORM_CAST (w unused) */
+int b200q_row_norm(const float* x_dev, const int32_t* rows_dev, int kind, const float* w_dev, void* y_dev, int n,
+                   int W, float eps, int dtype, void* stream);
+/* x[t] += mult * post(y[t] + bias) over fp32 rows x and model-dtype rows y (bias fp32 [W] or NULL; post_kind
+ * B200Q_NORM_DYT or B200Q_NORM_RMS with weights post_w), then out[t] = next(x[t]) in the model dtype (next_kind any
+ * B200Q_NORM_*; B200Q_NORM_NONE: no output) — the sum that closes a sublayer and the norm that opens the next */
+int b200q_sandwich_add(float* x_dev, const void* y_dev, const float* bias_dev, int post_kind, const float* post_w_dev,
+                       float mult, int next_kind, const float* next_w_dev, void* out_dev, int T, int W, float eps,
+                       int dtype, void* stream);
+/* v[i] *= a */
+int b200q_scale_f32(float* v_dev, int64_t n, float a, void* stream);
+/* gated unit: gate_up row = [g (F) | u (F)]; y = gelu_tanh(g) * u */
+int b200q_gelu_glu(const void* gate_up_dev, void* y_dev, int64_t rows, int F, int dtype, void* stream);
+/* per-layer token input: out[t, j] = gelu_tanh(g[t, j]) * table[id(t), col0 + j], j < D (ids < 0 as in b200q_embed_ex;
+ * g rows of stride ldg, table rows of stride ld_table, both in the model dtype) */
+int b200q_token_side_gate(const void* g_dev, int ldg, const int32_t* ids_dev, const int32_t* prev_out_dev,
+                          const void* table_dev, int ld_table, int col0, void* out_dev, int T, int D, int dtype,
+                          void* stream);
+/* b200q_window_attn_prep with options: proj row = [q | k | v] at q_off / k_off / v_off (k_off < 0: the layer reads
+ * another layer's cache and writes none); bias fp32 (indexed like a proj row) or NULL; qk_norm as in
+ * b200q_layer_desc with weights w_qn / w_kn, before rotation; sine and cosine times mag; the query at position p
+ * also times 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (temp_every 0: off) */
+int b200q_window_attn_prep_ex(const void* proj_dev, int ldp, int q_off, int k_off, int v_off, const float* bias_dev,
+                              int heads, int kv_heads, int dim, int vdim, int qk_norm, const float* w_qn_dev,
+                              const float* w_kn_dev, float eps, int rot_dims, const double* freq_dev, float mag,
+                              const int32_t* positions_dev, const int32_t* slot_mapping_dev, const float* temp_dev,
+                              float scale, float temp_coef, int temp_every, float* qs_dev, void* cache_dev, int T,
+                              int dtype, void* stream);
+/* b200q_window_attn with options: key j <= p is visible when p - j < window or j < keep_first (window 0: every
+ * j <= p); scores <- softcap * tanh(scores / softcap) before the softmax (softcap 0: off) */
+int b200q_window_attn_ex(const float* qs_dev, const void* cache_dev, const int32_t* block_table_dev, int bt_stride,
+                         const int32_t* row_seq_dev, const int32_t* positions_dev, const int32_t* seq_desc_dev,
+                         int n_seqs, int T, int heads, int kv_heads, int dim, int vdim, int block_size, int window,
+                         int keep_first, float softcap, const void* gate_dev, int ld_gate, void* out_dev, int dtype,
+                         void* stream);
+/* b200q_latent_prep with q_rank = 0 allowed (full-rank queries: no query latent) and sine / cosine times mag */
+int b200q_latent_prep_ex(const void* proj_dev, int ldp, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                         const double* freq_dev, float mag, const int32_t* positions_dev,
+                         const int32_t* slot_mapping_dev, const float* w_qn_dev, const float* w_kvn_dev, void* cq_dev,
+                         void* cache_dev, int has_kv, int T, float eps, int dtype, void* stream);
+/* b200q_rope_pairs_q over query rows of stride ldq, sine / cosine times mag */
+int b200q_rope_pairs_q_ex(const void* q_dev, int ldq, int heads, int dim, int rot_dim, int rot_dims,
+                          const double* freq_dev, float mag, const int32_t* positions_dev, float* qa_dev, int kv_rank,
+                          int T, int dtype, void* stream);
+/* b200q_latent_attn whose head outputs are multiplied by sigmoid(gate[t, h]) (model dtype rows of stride ld_gate; NULL:
+ * no gate) */
+int b200q_latent_attn_ex(const float* qa_dev, const void* cache_dev, const int32_t* block_table_dev, int bt_stride,
+                         const int32_t* row_seq_dev, const int32_t* positions_dev, int T, int heads, int kv_rank,
+                         int rot_dim, int block_size, int window, float scale, const void* gate_dev, int ld_gate,
+                         void* out_dev, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Model-level: one forward step over a mixed decode+prefill token batch.
  * Replaces GPUModelRunner.execute_model for LlamaForCausalLM
@@ -498,6 +556,11 @@ typedef struct b200q_model_config {
   int32_t token_shift;    /* pre-norm form, 1: the mixer reads h + (h_prev - h) * shift ("shift" [1, W] per layer),
                              h_prev = the previous token's normed row (zeros before the first token)           */
   float logit_softcap;    /* layered architectures: logits <- cap * tanh(logits / cap); 0 = off                */
+  /* sandwich form (zero elsewhere) */
+  int32_t norm_kind;      /* B200Q_NORM_RMS | B200Q_NORM_DYT: the norm on both sides of every sublayer and the final one */
+  float residual_mult;    /* every sublayer's normed output is multiplied by this before it joins x; 0 = 1      */
+  int32_t side_dim;       /* per-layer token input: columns of the second embedding table a layer reads; 0 = none */
+  float logit_scale;      /* layered architectures: logits are multiplied by this; 0 = 1                        */
 } b200q_model_config;
 
 #define B200Q_ARCH_LLAMA 0
@@ -517,9 +580,24 @@ typedef struct b200q_model_config {
  * before a layer (x <- W_in [x; x0]), a tied output matrix and soft-capped logits. */
 #define B200Q_ARCH_PALUZEN 4
 
+/* Kabavik: a layered decoder with a norm on BOTH sides of every sublayer and a residual multiplier m,
+ *   x <- x + m * norm1b(mixer(norm1 x));  x <- x + m * norm2b(ff(norm2 x));
+ *   x <- x + m * rms(P (gelu(G x) * e)) * s      (e = the layer's columns of a second embedding row of the token)
+ * with dynamic-tanh norms (tanh(alpha x) * w + b: no statistics of the row), grouped-query attention with biases,
+ * query / key norms, kept first keys behind the window, soft-capped scores, a query temperature that grows with the
+ * logarithm of the position, keys and values shared with an earlier layer; latent attention with full-rank queries,
+ * YaRN-scaled frequencies and a sigmoid gate per head; gated GELU feed-forwards; scaled logits. */
+#define B200Q_ARCH_KABAVIK 5
+
 #define B200Q_FORM_PARALLEL 0  /* x <- x + mixer(norm1 x) + ff(norm2 x)                                  */
 #define B200Q_FORM_POSTNORM 1  /* x <- norm1(alpha x + ls1 mixer(x~)); x <- norm2(alpha x + ls2 ff(x~)) */
 #define B200Q_FORM_PRENORM 2   /* x <- x + a mixer(h) (+ b side(h)), h = shift(norm1 x); x <- x + ff(norm2 x)     */
+#define B200Q_FORM_SANDWICH 3  /* x <- x + m norm1b(mixer(norm1 x)); x <- x + m norm2b(ff(norm2 x)) (+ token input) */
+
+#define B200Q_NORM_RMS 0       /* x / sqrt(mean(x^2) + eps) * w                                                    */
+#define B200Q_NORM_DYT 1       /* tanh(alpha * x) * w + b  (weights as one fp32 row [w (W) | b (W) | alpha])       */
+#define B200Q_NORM_CAST 2      /* op-level only: the row itself, in the model dtype                                */
+#define B200Q_NORM_NONE 3      /* op-level only: nothing                                                           */
 
 #define B200Q_DTYPE_BF16 0
 #define B200Q_DTYPE_F32 1
@@ -557,6 +635,7 @@ typedef struct b200q_model_config {
  * score = its largest choice score); weights = the chosen scores without correction, divided by their sum.  The
  * last `n_identity` router outputs are identity experts: they return their input.                               */
 #define B200Q_FF_MOE_GROUPED 5
+#define B200Q_FF_GEGLU 6            /* down(gelu_tanh(gate h) * up h); "mlp.gate_up" [2*ff, W] = gate rows, then up rows */
 
 typedef struct b200q_layer_desc {
   int32_t mixer;        /* B200Q_MIXER_*                                                               */
@@ -600,6 +679,24 @@ typedef struct b200q_layer_desc {
   int32_t side_vdim;
   int32_t side_decay_rank;
   float side_scale;
+  /* options of window attention and latent attention (zero = off) */
+  int32_t keep_first;   /* window attention: the first keep_first keys of a sequence stay visible behind the window  */
+  int32_t qk_norm;      /* window attention: RMS norm of q and k before rotation, plain weights "mix.q_norm" /
+                           "mix.k_norm": 1 = over the whole projection ([heads*dim], [kv_heads*dim]), 2 = per head
+                           (one [dim] weight shared by the heads)                                                  */
+  int32_t proj_bias;    /* window attention: 1 = q, k, v ("mix.proj_b" [rows of mix.proj]) and the output
+                           projection ("mix.o_b" [W]) have biases                                                  */
+  int32_t bare;         /* window attention: 1 = no temperature per head ("mix.temp") and no gate number per head
+                           (mix.proj = [q | k | v] rows, padded to a multiple of 64)                               */
+  int32_t head_gate;    /* latent attention: 1 = head h's output is multiplied by sigmoid of a gate number
+                           (mix.down gains `heads` rows behind the latents)                                        */
+  float q_temp_coef;    /* window attention: the query at position p is multiplied by                              */
+  int32_t q_temp_every; /*   1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1); q_temp_every 0 = off         */
+  /* rotation frequencies f_i = rot_base^(-2i/rot_dims), then: rot_factor > 0 and rot_original == 0: f_i / rot_factor;
+   * rot_original > 0 (YaRN): with dim(t) = rot_dims ln(rot_original / (2 pi t)) / (2 ln rot_base), lo = max(floor(
+   * dim(rot_fast)), 0), hi = min(ceil(dim(rot_slow)), rot_dims - 1), r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1):
+   * f_i / rot_factor * r_i + f_i (1 - r_i), and sine and cosine are multiplied by 0.1 ln(rot_factor) + 1 */
+  double rot_factor, rot_original, rot_fast, rot_slow;
 } b200q_layer_desc;
 
 typedef struct b200q_model* b200q_model_t;

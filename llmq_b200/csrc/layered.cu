@@ -49,17 +49,29 @@ int check_sequence_mixer(int i, const b200q_layer_desc& d) {
                         d.rot_dims <= d.dim && (d.rot_dims == 0 || d.rot_base > 0.0),
                     "layer %d: bad window-attention sizes (dim, vdim <= 512, even rot.dims <= dim, kv_heads divides heads)",
                     i);
+    B200Q_CHECK_ARG(d.keep_first >= 0 && d.qk_norm >= 0 && d.qk_norm <= 2 && d.softcap >= 0.f && d.q_temp_every >= 0 &&
+                        d.rot_factor >= 0.0 && d.rot_original >= 0.0 &&
+                        (d.bare || (d.proj_bias == 0 && d.qk_norm == 0 && d.q_temp_every == 0 && d.kv_from < 0)),
+                    "layer %d: bad window-attention options (biases, query / key norms, a query temperature by "
+                    "position and borrowed keys go with the bare projection layout)", i);
   }
   return B200Q_OK;
 }
 
 int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
   B200Q_CHECK_ARG(c && L, "layered config is null");
-  B200Q_CHECK_ARG(c->arch == B200Q_ARCH_RAMOPEL || c->arch == B200Q_ARCH_NORIDRA || c->arch == B200Q_ARCH_PALUZEN,
+  B200Q_CHECK_ARG(c->arch == B200Q_ARCH_RAMOPEL || c->arch == B200Q_ARCH_NORIDRA || c->arch == B200Q_ARCH_PALUZEN ||
+                      c->arch == B200Q_ARCH_KABAVIK,
                   "create_layered: arch=%d is not a layered architecture", c->arch);
   B200Q_CHECK_ARG(c->layer_form == B200Q_FORM_PARALLEL || c->layer_form == B200Q_FORM_POSTNORM ||
-                      c->layer_form == B200Q_FORM_PRENORM,
+                      c->layer_form == B200Q_FORM_PRENORM || c->layer_form == B200Q_FORM_SANDWICH,
                   "layer_form=%d unknown", c->layer_form);
+  const bool sandwich = c->layer_form == B200Q_FORM_SANDWICH;
+  B200Q_CHECK_ARG(sandwich ? ((c->norm_kind == B200Q_NORM_RMS || c->norm_kind == B200Q_NORM_DYT) && c->side_dim >= 0 &&
+                              c->residual_mult >= 0.f && c->learned_pos == 0)
+                           : (c->norm_kind == 0 && c->side_dim == 0 && c->residual_mult == 0.f),
+                  "norm kind (%d), residual multiplier and per-layer token input belong to the sandwich form",
+                  c->norm_kind);
   B200Q_CHECK_ARG(c->logit_softcap >= 0.f && (c->token_shift == 0 || c->layer_form == B200Q_FORM_PRENORM),
                   "bad logit soft cap, or a token shift outside the pre-norm form");
   B200Q_CHECK_ARG(c->norm_groups >= 0 && (c->norm_groups <= 1 || c->hidden % c->norm_groups == 0) &&
@@ -75,9 +87,12 @@ int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
     const b200q_layer_desc& d = L[i];
     if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
       B200Q_CHECK_ARG(d.heads > 0 && d.dim >= 0 && d.rot_dim >= 0 && d.dim + d.rot_dim > 0 && d.vdim > 0 &&
-                          d.q_rank > 0 && d.kv_rank > 0 && d.kv_rank <= 1024 && d.window >= 0 && d.rot_dims >= 0 &&
-                          d.rot_dims % 2 == 0 && d.rot_dims <= d.rot_dim,
+                          d.q_rank >= 0 && d.kv_rank > 0 && d.kv_rank <= 1024 && d.window >= 0 && d.rot_dims >= 0 &&
+                          d.rot_dims % 2 == 0 && d.rot_dims <= d.rot_dim && d.rot_factor >= 0.0 && d.rot_original >= 0.0,
                       "layer %d: bad latent attention sizes (kv_rank <= 1024, even rot.dims <= rot_dim)", i);
+      // full-rank queries (q_rank 0) and the gate number per head come as one fused projection of the layer's input
+      B200Q_CHECK_ARG((d.q_rank == 0) == (d.head_gate != 0) && (d.q_rank > 0 || d.kv_from < 0),
+                      "layer %d: full-rank queries (q_rank 0) come with a gate per head and latents of their own", i);
       if (d.kv_from >= 0) {
         B200Q_CHECK_ARG(d.kv_from < i && L[d.kv_from].mixer == B200Q_MIXER_LATENT_ATTN && L[d.kv_from].kv_from < 0 &&
                             L[d.kv_from].kv_rank == d.kv_rank && L[d.kv_from].rot_dim == d.rot_dim,
@@ -102,6 +117,13 @@ int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
     } else if (d.mixer == B200Q_MIXER_LIGHTNING || d.mixer == B200Q_MIXER_DECAY_MIX ||
                d.mixer == B200Q_MIXER_WINDOW_ATTN) {
       if (int rc = check_sequence_mixer(i, d)) return rc;
+      if (d.mixer == B200Q_MIXER_WINDOW_ATTN && d.kv_from >= 0) {
+        const b200q_layer_desc& o = L[d.kv_from < i ? d.kv_from : 0];
+        B200Q_CHECK_ARG(d.kv_from < i && o.mixer == B200Q_MIXER_WINDOW_ATTN && o.kv_from < 0 && o.kv_heads == d.kv_heads &&
+                            o.dim == d.dim && o.vdim == d.vdim,
+                        "layer %d: kv_from=%d must name an earlier window-attention layer with keys and values of its "
+                        "own and the same sizes", i, d.kv_from);
+      }
     } else {
       set_error("layer %d: unknown mixer %d", i, d.mixer);
       return B200Q_EINVAL;
@@ -113,7 +135,13 @@ int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
     }
     B200Q_CHECK_ARG((d.inject == 0 && d.side_mixer == 0 && d.mix_scale == 0.f) || c->layer_form == B200Q_FORM_PRENORM,
                     "layer %d: re-injection, side mixers and mixer scales belong to the pre-norm form", i);
-    if (d.ff == B200Q_FF_RELU2) {
+    B200Q_CHECK_ARG(!sandwich || d.ff == B200Q_FF_GEGLU || d.ff == B200Q_FF_NONE,
+                    "layer %d: feed-forward %d is not built for the sandwich form", i, d.ff);
+    B200Q_CHECK_ARG(!sandwich || d.mixer == B200Q_MIXER_LATENT_ATTN || d.mixer == B200Q_MIXER_WINDOW_ATTN,
+                    "layer %d: mixer %d is not built for the sandwich form", i, d.mixer);
+    if (d.ff == B200Q_FF_GEGLU) {
+      B200Q_CHECK_ARG(d.ff_dim > 0 && sandwich, "layer %d: bad gated-GELU feed-forward", i);
+    } else if (d.ff == B200Q_FF_RELU2) {
       B200Q_CHECK_ARG(d.ff_dim > 0 && c->layer_form == B200Q_FORM_PRENORM, "layer %d: bad squared-ReLU feed-forward", i);
     } else if (d.ff == B200Q_FF_MOE_GROUPED) {
       const int E = d.n_experts + d.n_identity;
@@ -148,6 +176,17 @@ struct Widths {
   bool moe = false, shared = false, hf = false, side = false, inject = false;
 };
 int64_t pad64(int64_t v) { return (v + 63) & ~(int64_t)63; }
+// rows of window attention's fused projection: [q | k | v (own keys and values) | gate number per head (not bare)],
+// with zero rows up to a multiple of 64
+int64_t window_proj_rows(const b200q_layer_desc& d) {
+  return pad64((int64_t)d.heads * d.dim + (d.kv_from < 0 ? (int64_t)d.kv_heads * (d.dim + d.vdim) : 0) +
+               (d.bare ? 0 : d.heads));
+}
+// rows of latent attention's fused projection with full-rank queries: [q | latent | shared rotated key | gate number
+// per head], with zero rows up to a multiple of 64
+int64_t latent_full_rows(const b200q_layer_desc& d) {
+  return pad64((int64_t)d.heads * (d.dim + d.rot_dim) + d.kv_rank + d.rot_dim + d.heads);
+}
 void sequence_mixer_widths(const b200q_layer_desc& d, int64_t W, Widths& w) {
   const int64_t HD = (int64_t)d.heads * d.dim, HV = (int64_t)d.heads * d.vdim;
   if (d.mixer == B200Q_MIXER_LIGHTNING) {
@@ -163,7 +202,7 @@ void sequence_mixer_widths(const b200q_layer_desc& d, int64_t W, Widths& w) {
     w.cvf = std::max<int64_t>(w.cvf, 5 * HD);  // r | k | v | w and the raw outputs
     w.attn = std::max<int64_t>(w.attn, HD);
   } else if (d.mixer == B200Q_MIXER_WINDOW_ATTN) {
-    w.proj = std::max<int64_t>(w.proj, pad64(HD + (int64_t)d.kv_heads * (d.dim + d.vdim) + d.heads));
+    w.proj = std::max<int64_t>(w.proj, window_proj_rows(d));
     w.qa = std::max<int64_t>(w.qa, HD);
     w.attn = std::max<int64_t>(w.attn, HV);
   }
@@ -174,9 +213,9 @@ Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_la
     const b200q_layer_desc& d = l.d;
     if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
       const int64_t RP = d.kv_rank + d.rot_dim;
-      w.proj = std::max<int64_t>(w.proj, d.q_rank + (d.kv_from < 0 ? RP : 0));
+      w.proj = std::max<int64_t>(w.proj, d.q_rank > 0 ? d.q_rank + (d.kv_from < 0 ? RP : 0) : latent_full_rows(d));
       w.cq = std::max<int64_t>(w.cq, d.q_rank);
-      w.q = std::max<int64_t>(w.q, (int64_t)d.heads * (d.dim + d.rot_dim));
+      if (d.q_rank > 0) w.q = std::max<int64_t>(w.q, (int64_t)d.heads * (d.dim + d.rot_dim));
       w.qa = std::max<int64_t>(w.qa, (int64_t)d.heads * RP);
       w.olat = std::max<int64_t>(w.olat, (int64_t)d.heads * d.kv_rank);
       w.attn = std::max<int64_t>(w.attn, (int64_t)d.heads * d.vdim);
@@ -209,7 +248,10 @@ Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_la
       sequence_mixer_widths(side_desc(d), c.hidden, w);
     }
     if (d.inject) w.inject = true;
-    if (d.ff == B200Q_FF_RELU2) {
+    if (d.ff == B200Q_FF_GEGLU) {
+      w.ffh = std::max<int64_t>(w.ffh, 2 * (int64_t)d.ff_dim);
+      w.ffa = std::max<int64_t>(w.ffa, d.ff_dim);
+    } else if (d.ff == B200Q_FF_RELU2) {
       w.ffh = std::max<int64_t>(w.ffh, d.ff_dim);
     } else if (d.ff == B200Q_FF_MOE_GROUPED) {
       w.moe = true;
@@ -293,10 +335,29 @@ int64_t layout(b200q_model* m, uint8_t* base) {
   y->carry = (float*)take(c.token_shift ? (int64_t)c.max_seqs * W * 4 : 1);
   y->mix2 = take(w.side ? T * W * es : 1);
   y->blend = take(w.blend ? T * w.blend * es : 1);
+  y->tg = take(c.side_dim > 0 ? T * c.side_dim * es : 1);
+  y->ta = take(c.side_dim > 0 ? T * c.side_dim * es : 1);
   y->sel = take(LR * W * es);
   y->logits = (float*)take(LR * (int64_t)c.vocab * 4);
   y->logits_bf16 = take((int64_t)c.max_seqs * c.vocab * 2);
   return off;
+}
+
+// the layer's rotation frequencies (fp64, on the device) and the factor of sine and cosine
+int upload_frequencies(b200q_layered_layer& l) {
+  const b200q_layer_desc& d = l.d;
+  const int half = d.rot_dims / 2;
+  if (half <= 0) return B200Q_OK;
+  std::vector<double> f(half);
+  int rc = b200q_rot_frequencies(d.rot_dims, d.rot_base, d.rot_factor, d.rot_original, d.rot_fast, d.rot_slow, f.data(),
+                                 &l.mag);
+  if (rc) return rc;
+  if (cudaMalloc(&l.freq, half * sizeof(double)) != cudaSuccess ||
+      cudaMemcpy(l.freq, f.data(), half * sizeof(double), cudaMemcpyHostToDevice) != cudaSuccess) {
+    set_error("create_layered: CUDA allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return B200Q_ECUDA;
+  }
+  return B200Q_OK;
 }
 
 }  // namespace
@@ -324,17 +385,9 @@ int layered_create(const b200q_model_config* cfg, const b200q_layer_desc* layers
       } else {
         l.cache_block_off = m->lay->layers[l.d.kv_from].cache_block_off;
       }
-      // rotation frequencies base^(-2i/dims), fp64
-      const int half = l.d.rot_dims / 2;
-      if (half > 0) {
-        std::vector<double> f(half);
-        for (int k = 0; k < half; ++k) f[k] = pow((double)l.d.rot_base, -2.0 * k / (double)l.d.rot_dims);
-        if (cudaMalloc(&l.freq, half * sizeof(double)) != cudaSuccess ||
-            cudaMemcpy(l.freq, f.data(), half * sizeof(double), cudaMemcpyHostToDevice) != cudaSuccess) {
-          set_error("create_layered: CUDA allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
-          b200q_model_destroy(m);
-          return B200Q_ECUDA;
-        }
+      if ((rc = upload_frequencies(l))) {
+        b200q_model_destroy(m);
+        return rc;
       }
     } else if (l.d.mixer == B200Q_MIXER_GENERAL_DELTA) {
       l.state_off = m->lay->state_slot_floats;
@@ -353,18 +406,15 @@ int layered_create(const b200q_model_config* cfg, const b200q_layer_desc* layers
       l.conv_off = m->lay->state_slot_floats;
       m->lay->state_slot_floats += (int64_t)(l.d.conv_taps - 1) * l.d.inner;
     } else if (l.d.mixer == B200Q_MIXER_WINDOW_ATTN) {
-      l.cache_block_off = m->lay->kv_block_bytes;
-      m->lay->kv_block_bytes += (int64_t)cfg->block_size * l.d.kv_heads * (l.d.dim + l.d.vdim) * es;
-      const int half = l.d.rot_dims / 2;
-      if (half > 0) {
-        std::vector<double> f(half);
-        for (int k = 0; k < half; ++k) f[k] = pow((double)l.d.rot_base, -2.0 * k / (double)l.d.rot_dims);
-        if (cudaMalloc(&l.freq, half * sizeof(double)) != cudaSuccess ||
-            cudaMemcpy(l.freq, f.data(), half * sizeof(double), cudaMemcpyHostToDevice) != cudaSuccess) {
-          set_error("create_layered: CUDA allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
-          b200q_model_destroy(m);
-          return B200Q_ECUDA;
-        }
+      if (l.d.kv_from < 0) {
+        l.cache_block_off = m->lay->kv_block_bytes;
+        m->lay->kv_block_bytes += (int64_t)cfg->block_size * l.d.kv_heads * (l.d.dim + l.d.vdim) * es;
+      } else {  // the keys and values of an earlier layer, as its cache holds them
+        l.cache_block_off = m->lay->layers[l.d.kv_from].cache_block_off;
+      }
+      if ((rc = upload_frequencies(l))) {
+        b200q_model_destroy(m);
+        return rc;
       }
     }
     if (l.d.side_mixer) {
@@ -431,8 +481,21 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
   };
   int rc;
   if (!strcmp(name, "embed")) { if ((rc = expect(c.vocab, W))) return rc; m->embed = p; return B200Q_OK; }
-  if (!strcmp(name, "final_norm")) { if ((rc = expect(1, W))) return rc; m->final_norm = p; return B200Q_OK; }
+  if (!strcmp(name, "final_norm")) {
+    const bool dyt = c.layer_form == B200Q_FORM_SANDWICH && c.norm_kind == B200Q_NORM_DYT;
+    if ((rc = expect(1, dyt ? 2 * W + 1 : W))) return rc;
+    m->final_norm = p;
+    return B200Q_OK;
+  }
   if (!strcmp(name, "lm_head")) { if ((rc = expect(c.vocab, W))) return rc; m->lm_head = p; return B200Q_OK; }
+  if (!strcmp(name, "tok_embed")) {
+    B200Q_CHECK_ARG(c.side_dim > 0 && rows == c.vocab && cols >= (int64_t)c.n_layers * c.side_dim,
+                    "weight tok_embed has shape [%lld,%lld], expected [%d, >= %lld]", (long long)rows, (long long)cols,
+                    c.vocab, (long long)c.n_layers * c.side_dim);
+    m->lay->tok_embed = p;
+    m->lay->tok_cols = cols;
+    return B200Q_OK;
+  }
   if (!strcmp(name, "pos")) {
     B200Q_CHECK_ARG(c.learned_pos && cols == W && rows >= c.max_pos, "weight pos has shape [%lld,%lld], expected [>= %d,%lld]",
                     (long long)rows, (long long)cols, c.max_pos, (long long)W);
@@ -454,6 +517,21 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
     if ((rc = expect((r), (cc)))) return rc;             \
     *(const void**)&(slot) = p;                          \
     return B200Q_OK;                                     \
+  }
+  if (c.layer_form == B200Q_FORM_SANDWICH) {
+    // norm rows: dynamic tanh [w | b | alpha], RMS [w]
+    const int64_t NW = c.norm_kind == B200Q_NORM_DYT ? 2 * W + 1 : W;
+    FIELD("norm1", l.norm1, 1, NW)
+    FIELD("norm1b", l.norm1b, 1, NW)
+    if (d.ff != B200Q_FF_NONE) {
+      FIELD("norm2", l.norm2, 1, NW)
+      FIELD("norm2b", l.norm2b, 1, NW)
+    }
+    if (c.side_dim > 0) {
+      FIELD("tok.gate", l.tok_gate, c.side_dim, W)
+      FIELD("tok.proj", l.tok_proj, W, c.side_dim)
+      FIELD("tok.norm", l.tok_norm, 1, W)
+    }
   }
   FIELD("norm1", l.norm1, 1, W)
   if (d.ff != B200Q_FF_NONE) FIELD("norm2", l.norm2, 1, W)
@@ -488,8 +566,16 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
       SUB("out_norm", q->out_norm, 1, QD)
       SUB("o", q->o, W, QD)
     } else if (e.mixer == B200Q_MIXER_WINDOW_ATTN) {
-      SUB("proj", q->proj, pad64(QD + (int64_t)e.kv_heads * (e.dim + e.vdim) + e.heads), W)
-      SUB("temp", q->temp, 1, e.heads)
+      SUB("proj", q->proj, window_proj_rows(e), W)
+      if (!e.bare) SUB("temp", q->temp, 1, e.heads)
+      if (e.proj_bias) {
+        SUB("proj_b", q->proj_b, 1, window_proj_rows(e))
+        SUB("o_b", q->o_b, 1, W)
+      }
+      if (e.qk_norm) {
+        SUB("q_norm", q->q_norm, 1, e.qk_norm == 1 ? QD : e.dim)
+        if (e.kv_from < 0) SUB("k_norm", q->kv_norm, 1, e.qk_norm == 1 ? (int64_t)e.kv_heads * e.dim : e.dim)
+      }
       SUB("o", q->o, W, QV)
     }
 #undef SUB
@@ -530,10 +616,14 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
     FIELD("mix.o", l.o, W, d.inner)
   } else if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
     const int64_t RP = d.kv_rank + d.rot_dim;
-    FIELD("mix.down", l.down, d.q_rank + (d.kv_from < 0 ? RP : 0), W)
-    FIELD("mix.q_norm", l.q_norm, 1, d.q_rank)
+    if (d.q_rank > 0) {
+      FIELD("mix.down", l.down, d.q_rank + (d.kv_from < 0 ? RP : 0), W)
+      FIELD("mix.q_norm", l.q_norm, 1, d.q_rank)
+      FIELD("mix.uq", l.uq, (int64_t)d.heads * (d.dim + d.rot_dim), d.q_rank)
+    } else {
+      FIELD("mix.down", l.down, latent_full_rows(d), W)
+    }
     if (d.kv_from < 0) FIELD("mix.kv_norm", l.kv_norm, 1, d.kv_rank)
-    FIELD("mix.uq", l.uq, (int64_t)d.heads * (d.dim + d.rot_dim), d.q_rank)
     FIELD("mix.uk_t", l.uk_t, (int64_t)d.heads * d.kv_rank, d.dim)
     FIELD("mix.uv", l.uv, (int64_t)d.heads * d.vdim, d.kv_rank)
     FIELD("mix.o", l.o, W, (int64_t)d.heads * d.vdim)
@@ -545,7 +635,10 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
     FIELD("mix.out_norm", l.out_norm, 1, HD)
     FIELD("mix.o", l.o, W, HD)
   }
-  if (d.ff == B200Q_FF_RELU2) {
+  if (d.ff == B200Q_FF_GEGLU) {
+    FIELD("mlp.gate_up", l.gate_up, 2 * (int64_t)d.ff_dim, W)
+    FIELD("mlp.down", l.ff_down, W, d.ff_dim)
+  } else if (d.ff == B200Q_FF_RELU2) {
     FIELD("mlp.up", l.up, d.ff_dim, W)
     FIELD("mlp.down", l.ff_down, W, d.ff_dim)
   } else if (d.ff == B200Q_FF_MOE_GROUPED) {
@@ -596,7 +689,7 @@ static int check_bound(b200q_model* m) {
     }
     if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
       need_kv = true;
-      ok = ok && l.down && l.q_norm && (d.kv_from >= 0 || l.kv_norm) && l.uq && l.uk_t && l.uv;
+      ok = ok && l.down && (d.q_rank == 0 || (l.q_norm && l.uq)) && (d.kv_from >= 0 || l.kv_norm) && l.uk_t && l.uv;
     } else if (d.mixer == B200Q_MIXER_GENERAL_DELTA) {
       need_state = true;
       ok = ok && l.proj && l.w2 && l.w0 && l.a_bias && l.out_norm;
@@ -626,10 +719,15 @@ static int check_bound(b200q_model* m) {
         ok = ok && q->mu && q->proj && q->w1 && q->w2 && q->w0 && q->bonus && q->out_norm;
       } else if (q->d.mixer == B200Q_MIXER_WINDOW_ATTN) {
         need_kv = true;
-        ok = ok && q->proj && q->temp;
+        ok = ok && q->proj && (q->d.bare || q->temp) && (!q->d.proj_bias || (q->proj_b && q->o_b)) &&
+             (!q->d.qk_norm || (q->q_norm && (q->d.kv_from >= 0 || q->kv_norm)));
       }
     }
     if (d.ff == B200Q_FF_RELU2) ok = ok && l.up && l.ff_down;
+    if (d.ff == B200Q_FF_GEGLU) ok = ok && l.gate_up && l.ff_down;
+    if (m->cfg.layer_form == B200Q_FORM_SANDWICH)
+      ok = ok && l.norm1b && (d.ff == B200Q_FF_NONE || l.norm2b) &&
+           (m->cfg.side_dim == 0 || (l.tok_gate && l.tok_proj && l.tok_norm && m->lay->tok_embed));
     if (d.ff == B200Q_FF_MOE_GROUPED)
       ok = ok && l.router && l.router_bias && (d.n_experts == 0 || (l.experts_up && l.experts_down));
     if (d.ff == B200Q_FF_MOE_SIGMOID) ok = ok && l.router && l.experts_gate_up && l.experts_down;
@@ -682,7 +780,9 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
       b200q_linear((Aptr), (lda), (Wptr), (bias), (Cptr), (ldc), T, (N), (K), dt, (f32), stream))
   const int EW = B200Q_PROF_ELEMENTWISE;
 
-  const bool post = c.layer_form == B200Q_FORM_POSTNORM, pre = c.layer_form == B200Q_FORM_PRENORM;
+  const bool post = c.layer_form == B200Q_FORM_POSTNORM, pre = c.layer_form == B200Q_FORM_PRENORM,
+             sandwich = c.layer_form == B200Q_FORM_SANDWICH;
+  const float mult = c.residual_mult > 0.f ? c.residual_mult : 1.f;
   const int groups = c.norm_groups > 0 ? c.norm_groups : 1;
   if (c.learned_pos)
     TRY(EW, (double)T * W * (2 * es + 4),
@@ -736,17 +836,27 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
                               y->attn, T, dt, stream));
       LIN(y->attn, HD, l.o, nullptr, outp, W, W, HD, 0);
     } else {  // B200Q_MIXER_WINDOW_ATTN
-      const int G = d.kv_heads, GD = G * d.dim, GV = G * d.vdim, NP = (int)pad64(HD + GD + GV + H);
-      uint8_t* cache = m->kv + m->num_blocks * l.cache_block_off;
-      LIN(y->h1, W, l.proj, nullptr, y->proj, NP, NP, W, 0);  // [q | k | v | gate number per head | zero rows]
-      TRY(EW, (double)T * ((HD + 2 * GD + 2 * GV) * es + HD * 4),
-          b200q_window_attn_prep(y->proj, NP, H, G, d.dim, d.vdim, d.rot_dims, l.freq, b->positions, b->slot_mapping,
-                                 l.temp, d.attn_scale, y->qa, cache, T, dt, stream));
+      const int G = d.kv_heads, GD = G * d.dim, GV = G * d.vdim, NP = (int)window_proj_rows(d);
+      const bool own = d.kv_from < 0;
+      const int n_kv = own ? GD + GV : 0;
+      uint8_t* cache = m->kv + m->num_blocks * l.cache_block_off;  // a borrowing layer's offset is the lender's
+      // [q | k | v (own keys and values) | gate number per head (not bare) | zero rows]; biases join in the next step
+      LIN(y->h1, W, l.proj, nullptr, y->proj, NP, NP, W, 0);
+      if (!d.bare && d.rot_factor == 0.0)
+        TRY(EW, (double)T * ((HD + 2 * GD + 2 * GV) * es + HD * 4),
+            b200q_window_attn_prep(y->proj, NP, H, G, d.dim, d.vdim, d.rot_dims, l.freq, b->positions, b->slot_mapping,
+                                   l.temp, d.attn_scale, y->qa, cache, T, dt, stream));
+      else
+        TRY(EW, (double)T * ((HD + 2 * n_kv) * es + HD * 4),
+            b200q_window_attn_prep_ex(y->proj, NP, 0, own ? HD : -1, HD + GD, d.proj_bias ? l.proj_b : nullptr, H, G,
+                                      d.dim, d.vdim, d.qk_norm, l.q_norm, l.kv_norm, c.rms_eps, d.rot_dims, l.freq, l.mag,
+                                      b->positions, b->slot_mapping, d.bare ? nullptr : l.temp, d.attn_scale,
+                                      d.q_temp_coef, d.q_temp_every, y->qa, cache, T, dt, stream));
       TRY(B200Q_PROF_DECODE_ATTN, (double)b->sum_ctx_dec * (GD + GV) * es,
-          b200q_window_attn(y->qa, cache, b->block_table, b->bt_stride, b->row_seq, b->positions, b->seq_desc, b->n_rows,
-                            T, H, G, d.dim, d.vdim, c.block_size, d.window, (uint8_t*)y->proj + (size_t)(HD + GD + GV) * es,
-                            NP, y->attn, dt, stream));
-      LIN(y->attn, HV, l.o, nullptr, outp, W, W, HV, 0);
+          b200q_window_attn_ex(y->qa, cache, b->block_table, b->bt_stride, b->row_seq, b->positions, b->seq_desc,
+                               b->n_rows, T, H, G, d.dim, d.vdim, c.block_size, d.window, d.keep_first, d.softcap,
+                               d.bare ? nullptr : (uint8_t*)y->proj + (size_t)(HD + n_kv) * es, NP, y->attn, dt, stream));
+      LIN(y->attn, HV, l.o, nullptr, outp, W, W, HV, 0);  // the output bias, if any, joins in the layer's sum
     }
     return B200Q_OK;
   };
@@ -758,26 +868,42 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
       return run_sequence_mixer(l, y->mix);
     if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
       const int R = d.kv_rank, P = d.rot_dim, RP = R + P, H = d.heads, QD = d.dim + P;
-      const bool own = d.kv_from < 0;
-      const int nd = d.q_rank + (own ? RP : 0);
+      const bool own = d.kv_from < 0, full = d.q_rank == 0;
       uint8_t* cache = m->kv + m->num_blocks * l.cache_block_off;
-      LIN(y->h1, W, l.down, nullptr, y->proj, nd, nd, W, 0);
-      TRY(EW, (double)T * (nd + d.q_rank + RP) * es,
-          b200q_latent_prep(y->proj, nd, d.q_rank, R, P, d.rot_dims, l.freq, b->positions, b->slot_mapping, l.q_norm,
-                            l.kv_norm, y->cq, cache, own ? 1 : 0, T, c.rms_eps, dt, stream));
-      LIN(y->cq, d.q_rank, l.uq, nullptr, y->q, H * QD, H * QD, d.q_rank, 0);
+      const void* q = y->q;   // the heads' queries [unrotated | rotated], rows of stride ldq
+      int ldq = H * QD;
+      const void* gate = nullptr;  // one gate number per head, rows of stride ldq
+      if (full) {
+        // full-rank queries: one projection of the layer's input gives [q | latent | shared rotated key | gates]
+        const int nd = (int)latent_full_rows(d);
+        LIN(y->h1, W, l.down, nullptr, y->proj, nd, nd, W, 0);
+        TRY(EW, (double)T * 2 * RP * es,
+            b200q_latent_prep_ex((uint8_t*)y->proj + (size_t)H * QD * es, nd, 0, R, P, d.rot_dims, l.freq, l.mag,
+                                 b->positions, b->slot_mapping, nullptr, l.kv_norm, nullptr, cache, 1, T, c.rms_eps, dt,
+                                 stream));
+        q = y->proj;
+        ldq = nd;
+        gate = (uint8_t*)y->proj + (size_t)(H * QD + RP) * es;
+      } else {
+        const int nd = d.q_rank + (own ? RP : 0);
+        LIN(y->h1, W, l.down, nullptr, y->proj, nd, nd, W, 0);
+        TRY(EW, (double)T * (nd + d.q_rank + RP) * es,
+            b200q_latent_prep_ex(y->proj, nd, d.q_rank, R, P, d.rot_dims, l.freq, l.mag, b->positions, b->slot_mapping,
+                                 l.q_norm, l.kv_norm, y->cq, cache, own ? 1 : 0, T, c.rms_eps, dt, stream));
+        LIN(y->cq, d.q_rank, l.uq, nullptr, y->q, H * QD, H * QD, d.q_rank, 0);
+      }
       TRY(EW, (double)T * H * P * (es + 4),
-          b200q_rope_pairs_q(y->q, H, d.dim, P, d.rot_dims, l.freq, b->positions, y->qa, R, T, dt, stream));
+          b200q_rope_pairs_q_ex(q, ldq, H, d.dim, P, d.rot_dims, l.freq, l.mag, b->positions, y->qa, R, T, dt, stream));
       // the unrotated query of every head, carried into the latent space: qa[t,h,:R] = W_uk[h]^T q[t,h,:dim]
       if (d.dim > 0)
         TRY(B200Q_PROF_GEMM, 2.0 * T * H * (double)R * d.dim,
-            b200q_linear_batched(y->q, H * QD, QD, l.uk_t, (long long)R * d.dim, y->qa, H * RP, RP, T, R, d.dim, H, dt,
-                                 1, stream));
+            b200q_linear_batched(q, ldq, QD, l.uk_t, (long long)R * d.dim, y->qa, H * RP, RP, T, R, d.dim, H, dt, 1,
+                                 stream));
       else
         B200Q_CUDA(cudaMemsetAsync(y->qa, 0, (size_t)T * H * RP * 4, cst));
       TRY(B200Q_PROF_DECODE_ATTN, 0.0,
-          b200q_latent_attn(y->qa, cache, b->block_table, b->bt_stride, b->row_seq, b->positions, T, H, R, P,
-                            c.block_size, d.window, d.attn_scale, y->olat, dt, stream));
+          b200q_latent_attn_ex(y->qa, cache, b->block_table, b->bt_stride, b->row_seq, b->positions, T, H, R, P,
+                               c.block_size, d.window, d.attn_scale, gate, ldq, y->olat, dt, stream));
       TRY(B200Q_PROF_GEMM, 2.0 * T * H * (double)R * d.vdim,
           b200q_linear_batched(y->olat, H * R, R, l.uv, (long long)d.vdim * R, y->attn, H * d.vdim, d.vdim, T, d.vdim, R,
                                H, dt, 0, stream));
@@ -925,6 +1051,47 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
       if (y->tap) TRY(EW, 8.0 * T * W, b200q_copy_f32(y->x, y->tap + (int64_t)li * T * W, (int64_t)T * W, stream));
       continue;
     }
+    if (sandwich) {
+      // x <- x + m n1b(mixer(n1 x) + o_b);  x <- x + m n2b(ff(n2 x));  x <- x + m rms(P (gelu(G x) * e)) s.
+      // Every sum also writes what reads the new x next: the following norm's output, or x itself in the model dtype.
+      const int NK = c.norm_kind, D = c.side_dim;
+      const bool last = li + 1 == c.n_layers;
+      const int next_kind = last ? B200Q_NORM_NONE : NK;
+      const float* next_w = last ? nullptr : y->layers[li + 1].norm1;
+      if (li == 0)
+        TRY(EW, (double)T * W * (4 + es), b200q_row_norm(y->x, nullptr, NK, l.norm1, y->h1, T, W, c.rms_eps, dt, stream));
+      if ((rc = run_mixer(l))) return rc;
+      const float* o_b = d.mixer == B200Q_MIXER_WINDOW_ATTN && d.proj_bias ? l.o_b : nullptr;
+      const int after_kind = D > 0 ? B200Q_NORM_CAST : next_kind;  // what follows the layer's last sublayer
+      const float* after_w = D > 0 ? nullptr : next_w;
+      if (has_ff) {
+        const int F = d.ff_dim;
+        TRY(EW, (double)T * W * (8 + 2 * es),
+            b200q_sandwich_add(y->x, y->mix, o_b, NK, l.norm1b, mult, NK, l.norm2, y->h2, T, W, c.rms_eps, dt, stream));
+        LIN(y->h2, W, l.gate_up, nullptr, y->ffh, 2 * F, 2 * F, W, 0);  // [gate | up]
+        TRY(EW, 3.0 * T * F * es, b200q_gelu_glu(y->ffh, y->ffa, T, F, dt, stream));
+        LIN(y->ffa, F, l.ff_down, nullptr, y->ffo, W, W, F, 0);
+        TRY(EW, (double)T * W * (8 + 2 * es),
+            b200q_sandwich_add(y->x, y->ffo, nullptr, NK, l.norm2b, mult, after_kind, after_w, y->h1, T, W, c.rms_eps, dt,
+                               stream));
+      } else {
+        TRY(EW, (double)T * W * (8 + 2 * es),
+            b200q_sandwich_add(y->x, y->mix, o_b, NK, l.norm1b, mult, after_kind, after_w, y->h1, T, W, c.rms_eps, dt,
+                               stream));
+      }
+      if (D > 0) {  // the per-layer token input reads x (in y->h1, model dtype) and the layer's columns of the table
+        LIN(y->h1, W, l.tok_gate, nullptr, y->tg, D, D, W, 0);
+        TRY(EW, (double)T * D * 3 * es,
+            b200q_token_side_gate(y->tg, D, b->token_ids, b->prev_out_ids, y->tok_embed, (int)y->tok_cols, li * D, y->ta,
+                                  T, D, dt, stream));
+        LIN(y->ta, D, l.tok_proj, nullptr, y->ffo, W, W, D, 0);
+        TRY(EW, (double)T * W * (8 + 2 * es),
+            b200q_sandwich_add(y->x, y->ffo, nullptr, B200Q_NORM_RMS, l.tok_norm, mult, next_kind, next_w, y->h1, T, W,
+                               c.rms_eps, dt, stream));
+      }
+      if (y->tap) TRY(EW, 8.0 * T * W, b200q_copy_f32(y->x, y->tap + (int64_t)li * T * W, (int64_t)T * W, stream));
+      continue;
+    }
     if (post) {
       // x <- norm1(alpha x + ls1 * mixer(x + conv1 x));  x <- norm2(alpha x + ls2 * ff(x + conv2 x))
       for (int sub = 0; sub < (has_ff ? 2 : 1); ++sub) {
@@ -1003,7 +1170,11 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
   }
   if (b->n_sample > 0) {
     const int n = b->n_sample;
-    if (post)
+    if (sandwich)
+      TRY(EW, (double)n * W * (4 + es),
+          b200q_row_norm(y->x, b->sample_rows, c.norm_kind, (const float*)m->final_norm, y->sel, n, W, c.rms_eps, dt,
+                         stream));
+    else if (post)
       TRY(EW, (double)n * W * (4 + es),
           b200q_group_rmsnorm(y->x, b->sample_rows, nullptr, nullptr, 0, nullptr, 1.f, (const float*)m->final_norm, groups,
                               c.rms_eps, nullptr, y->sel, n, W, dt, stream));
@@ -1017,6 +1188,8 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
                                  c.rms_eps, dt, stream));
     TRY(B200Q_PROF_GEMM, 2.0 * n * (double)c.vocab * W,
         b200q_linear(y->sel, W, m->lm_head, nullptr, y->logits, c.vocab, n, c.vocab, W, dt, 1, stream));
+    if (c.logit_scale > 0.f && c.logit_scale != 1.f)
+      TRY(EW, 8.0 * n * c.vocab, b200q_scale_f32(y->logits, (int64_t)n * c.vocab, c.logit_scale, stream));
     if (c.logit_softcap > 0.f)
       TRY(EW, 8.0 * n * c.vocab, b200q_softcap_f32(y->logits, (int64_t)n * c.vocab, c.logit_softcap, stream));
     if (!b->no_sampling) {

@@ -214,19 +214,21 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const T* __restrict__ 
                                                           const int32_t* __restrict__ slot_mapping,
                                                           const float* __restrict__ w_qn,
                                                           const float* __restrict__ w_kvn, T* __restrict__ cq,
-                                                          T* __restrict__ cache, int has_kv, float eps) {
+                                                          T* __restrict__ cache, int has_kv, float eps, float mag) {
   __shared__ float red[32];
   const int t = blockIdx.x;
   const T* pr = proj + (long long)t * ldp;
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) {
-    const float v = ldf(pr + c);
-    ss += v * v;
+  float ss = 0.f, inv;
+  if (q_rank > 0) {  // q_rank 0: full-rank queries, no query latent
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x) {
+      const float v = ldf(pr + c);
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    inv = 1.f / sqrtf(ss / (float)q_rank + eps);
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x)
+      stf(cq + (long long)t * q_rank + c, ldf(pr + c) * inv * w_qn[c]);
   }
-  ss = block_sum(ss, red);
-  float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
-  for (int c = threadIdx.x; c < q_rank; c += blockDim.x)
-    stf(cq + (long long)t * q_rank + c, ldf(pr + c) * inv * w_qn[c]);
   if (!has_kv) return;
   const int slot = slot_mapping[t];
   if (slot < 0) return;
@@ -245,7 +247,7 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const T* __restrict__ 
   for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
     double sn, cs;
     sincos(pos * freq[i], &sn, &cs);
-    const float u = ldf(pk + 2 * i), v = ldf(pk + 2 * i + 1), c = (float)cs, s = (float)sn;
+    const float u = ldf(pk + 2 * i), v = ldf(pk + 2 * i + 1), c = (float)cs * mag, s = (float)sn * mag;
     stf(row + kv_rank + 2 * i, u * c - v * s);
     stf(row + kv_rank + 2 * i + 1, v * c + u * s);
   }
@@ -258,21 +260,21 @@ template <typename T>
 __global__ void __launch_bounds__(128) rope_q_kernel(const T* __restrict__ q, int heads, int dim, int rot_dim,
                                                      int rot_dims, const double* __restrict__ freq,
                                                      const int32_t* __restrict__ positions,
-                                                     float* __restrict__ qa, int kv_rank) {
+                                                     float* __restrict__ qa, int kv_rank, int ldq, float mag) {
   extern __shared__ float cs_sn[];  // [rot_dims/2][2]
   const int t = blockIdx.x, half = rot_dims / 2;
   const double pos = (double)positions[t];
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     double sn, cs;
     sincos(pos * freq[i], &sn, &cs);
-    cs_sn[2 * i] = (float)cs;
-    cs_sn[2 * i + 1] = (float)sn;
+    cs_sn[2 * i] = (float)cs * mag;
+    cs_sn[2 * i + 1] = (float)sn * mag;
   }
   __syncthreads();
   const int RP = kv_rank + rot_dim;
   for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
     const int h = e / half, i = e % half;
-    const T* src = q + ((long long)t * heads + h) * (dim + rot_dim) + dim;
+    const T* src = q + (long long)t * ldq + (long long)h * (dim + rot_dim) + dim;
     float* dst = qa + ((long long)t * heads + h) * RP + kv_rank;
     const float u = ldf(src + 2 * i), v = ldf(src + 2 * i + 1), c = cs_sn[2 * i], s = cs_sn[2 * i + 1];
     dst[2 * i] = u * c - v * s;
@@ -281,7 +283,7 @@ __global__ void __launch_bounds__(128) rope_q_kernel(const T* __restrict__ q, in
   const int rest = rot_dim - rot_dims;
   for (int e = threadIdx.x; e < heads * rest; e += blockDim.x) {
     const int h = e / rest, j = rot_dims + e % rest;
-    qa[((long long)t * heads + h) * RP + kv_rank + j] = ldf(q + ((long long)t * heads + h) * (dim + rot_dim) + dim + j);
+    qa[((long long)t * heads + h) * RP + kv_rank + j] = ldf(q + (long long)t * ldq + (long long)h * (dim + rot_dim) + dim + j);
   }
 }
 
@@ -303,7 +305,8 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
                                                           const int32_t* __restrict__ row_seq,
                                                           const int32_t* __restrict__ positions, int heads,
                                                           int kv_rank, int rot_dim, int block_size, int window,
-                                                          float scale, T* __restrict__ out) {
+                                                          float scale, const T* __restrict__ gate, int ld_gate,
+                                                          T* __restrict__ out) {
   extern __shared__ float sm[];
   const int RP = kv_rank + rot_dim, KS = RP + 1;
   float* qs = sm;            // [8][RP]
@@ -359,7 +362,7 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
     m = m_new;
   }
   if (!live) return;
-  const float inv = 1.f / l;
+  const float inv = (gate ? sigmoidf_(ldf(gate + (long long)t * ld_gate + h)) : 1.f) / l;
   T* o = out + ((long long)t * heads + h) * kv_rank;
 #pragma unroll
   for (int i = 0; i < LATENT_ACC; ++i) {
@@ -396,6 +399,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const float* __res
                                                               const int32_t* __restrict__ row_seq,
                                                               const int32_t* __restrict__ positions, int heads, int R,
                                                               int P, int block_size, int window, float scale,
+                                                              const bf16* __restrict__ gate, int ld_gate,
                                                               bf16* __restrict__ out) {
   extern __shared__ __align__(16) uint8_t smraw[];
   const int RP = R + P, LDS = RP + 8;
@@ -549,7 +553,12 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const float* __res
       }
     }
   }
-  const float inv[2] = {1.f / l_[0], 1.f / l_[1]};
+  float inv[2] = {1.f / l_[0], 1.f / l_[1]};
+  if (gate) {  // one sigmoid gate number per head
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+      if (h0 + g + 8 * r < heads) inv[r] *= sigmoidf_(ldf(gate + (long long)t * ld_gate + h0 + g + 8 * r));
+  }
 #pragma unroll
   for (int i = 0; i < NTW; ++i) {
     if (i < ntw) {
@@ -581,6 +590,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma2_kernel(const float* __re
                                                                const int32_t* __restrict__ row_seq,
                                                                const int32_t* __restrict__ positions, int heads, int R,
                                                                int P, int block_size, int window, float scale,
+                                                               const bf16* __restrict__ gate, int ld_gate,
                                                                bf16* __restrict__ out) {
   extern __shared__ __align__(16) uint8_t smraw[];
   const int RP = R + P, LDS = RP + 8;
@@ -748,7 +758,12 @@ __global__ void __launch_bounds__(128) latent_attn_mma2_kernel(const float* __re
       }
     }
   }
-  const float inv[2] = {1.f / l_[0], 1.f / l_[1]};
+  float inv[2] = {1.f / l_[0], 1.f / l_[1]};
+  if (gate) {  // one sigmoid gate number per head
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+      if (h0 + g + 8 * r < heads) inv[r] *= sigmoidf_(ldf(gate + (long long)t * ld_gate + h0 + g + 8 * r));
+  }
 #pragma unroll
   for (int i = 0; i < NTW; ++i) {
     if (i < ntw) {
@@ -1351,27 +1366,45 @@ int b200q_latent_prep(const void* proj, int ldp, int q_rank, int kv_rank, int ro
                       const double* freq, const int32_t* positions, const int32_t* slot_mapping,
                       const float* w_qn, const float* w_kvn, void* cq, void* cache, int has_kv, int T_, float eps,
                       int dtype, void* stream) {
-  B200Q_CHECK_ARG(proj && w_qn && cq && positions && q_rank > 0 && is_dtype(dtype) && T_ >= 0,
+  B200Q_CHECK_ARG(q_rank > 0, "latent_prep: bad argument");
+  return b200q_latent_prep_ex(proj, ldp, q_rank, kv_rank, rot_dim, rot_dims, freq, 1.f, positions, slot_mapping, w_qn,
+                              w_kvn, cq, cache, has_kv, T_, eps, dtype, stream);
+}
+
+int b200q_latent_prep_ex(const void* proj, int ldp, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                         const double* freq, float mag, const int32_t* positions, const int32_t* slot_mapping,
+                         const float* w_qn, const float* w_kvn, void* cq, void* cache, int has_kv, int T_, float eps,
+                         int dtype, void* stream) {
+  B200Q_CHECK_ARG(proj && positions && q_rank >= 0 && (q_rank == 0 || (w_qn && cq)) && (q_rank > 0 || has_kv) &&
+                      is_dtype(dtype) && T_ >= 0,
                   "latent_prep: bad argument");
-  B200Q_CHECK_ARG(!has_kv || (cache && slot_mapping && w_kvn && freq && kv_rank > 0 && rot_dim >= 0 &&
+  B200Q_CHECK_ARG(!has_kv || (cache && slot_mapping && w_kvn && (freq || rot_dims == 0) && kv_rank > 0 && rot_dim >= 0 &&
                               rot_dims % 2 == 0 && rot_dims <= rot_dim),
                   "latent_prep: bad cache arguments (kv_rank=%d rot_dim=%d rot_dims=%d)", kv_rank, rot_dim, rot_dims);
   if (T_ == 0) return B200Q_OK;
   DISPATCH_T(dtype, (latent_prep_kernel<T><<<T_, 128, 0, as_stream(stream)>>>(
                         (const T*)proj, ldp, q_rank, kv_rank, rot_dim, rot_dims, freq, positions, slot_mapping, w_qn,
-                        w_kvn, (T*)cq, (T*)cache, has_kv, eps)));
+                        w_kvn, (T*)cq, (T*)cache, has_kv, eps, mag)));
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
 
 int b200q_rope_pairs_q(const void* q, int heads, int dim, int rot_dim, int rot_dims, const double* freq,
                        const int32_t* positions, float* qa, int kv_rank, int T_, int dtype, void* stream) {
-  B200Q_CHECK_ARG(q && freq && positions && qa && heads > 0 && dim >= 0 && rot_dims % 2 == 0 && rot_dims <= rot_dim &&
+  return b200q_rope_pairs_q_ex(q, heads * (dim + rot_dim), heads, dim, rot_dim, rot_dims, freq, 1.f, positions, qa, kv_rank,
+                               T_, dtype, stream);
+}
+
+int b200q_rope_pairs_q_ex(const void* q, int ldq, int heads, int dim, int rot_dim, int rot_dims, const double* freq,
+                          float mag, const int32_t* positions, float* qa, int kv_rank, int T_, int dtype, void* stream) {
+  B200Q_CHECK_ARG(ldq >= heads * (dim + rot_dim), "rope_pairs_q: row stride %d below the heads' %d values", ldq,
+                  heads * (dim + rot_dim));
+  B200Q_CHECK_ARG(q && (freq || rot_dims == 0) && positions && qa && heads > 0 && dim >= 0 && rot_dims % 2 == 0 && rot_dims <= rot_dim &&
                       is_dtype(dtype) && T_ >= 0,
                   "rope_pairs_q: bad argument");
   if (T_ == 0 || rot_dim == 0) return B200Q_OK;
   DISPATCH_T(dtype, (rope_q_kernel<T><<<T_, 128, (size_t)(rot_dims + 2) * sizeof(float), as_stream(stream)>>>(
-                        (const T*)q, heads, dim, rot_dim, rot_dims, freq, positions, qa, kv_rank)));
+                        (const T*)q, heads, dim, rot_dim, rot_dims, freq, positions, qa, kv_rank, ldq, mag)));
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -1379,6 +1412,15 @@ int b200q_rope_pairs_q(const void* q, int heads, int dim, int rot_dim, int rot_d
 int b200q_latent_attn(const float* qa, const void* cache, const int32_t* block_table, int bt_stride,
                       const int32_t* row_seq, const int32_t* positions, int T_, int heads, int kv_rank, int rot_dim,
                       int block_size, int window, float scale, void* out, int dtype, void* stream) {
+  return b200q_latent_attn_ex(qa, cache, block_table, bt_stride, row_seq, positions, T_, heads, kv_rank, rot_dim, block_size,
+                              window, scale, nullptr, 0, out, dtype, stream);
+}
+
+int b200q_latent_attn_ex(const float* qa, const void* cache, const int32_t* block_table, int bt_stride,
+                         const int32_t* row_seq, const int32_t* positions, int T_, int heads, int kv_rank, int rot_dim,
+                         int block_size, int window, float scale, const void* gate, int ld_gate, void* out, int dtype,
+                         void* stream) {
+  B200Q_CHECK_ARG(!gate || ld_gate >= heads, "latent_attn: gate rows of stride %d hold fewer than %d heads", ld_gate, heads);
   B200Q_CHECK_ARG(qa && cache && block_table && row_seq && positions && out && heads > 0 && T_ >= 0 &&
                       block_size > 0 && window >= 0 && is_dtype(dtype),
                   "latent_attn: bad argument");
@@ -1407,7 +1449,7 @@ int b200q_latent_attn(const float* qa, const void* cache, const int32_t* block_t
                                     (int)sm3));                                                                   \
     latent_attn_mma2_kernel<NTW, KS><<<grid2, 128, sm3, as_stream(stream)>>>(                                      \
         qa, (const bf16*)cache, block_table, bt_stride, row_seq, positions, heads, kv_rank, rot_dim, block_size, \
-        window, scale, (bf16*)out);                                                                               \
+        window, scale, (const bf16*)gate, ld_gate, (bf16*)out);                                                   \
     B200Q_LAUNCH_CHECK();                                                                                         \
     return B200Q_OK;                                                                                              \
   } while (0)
@@ -1424,7 +1466,7 @@ int b200q_latent_attn(const float* qa, const void* cache, const int32_t* block_t
                                     (int)sm2));                                                                   \
     latent_attn_mma_kernel<NTW><<<grid2, 128, sm2, as_stream(stream)>>>(                                          \
         qa, (const bf16*)cache, block_table, bt_stride, row_seq, positions, heads, kv_rank, rot_dim, block_size, \
-        window, scale, (bf16*)out);                                                                               \
+        window, scale, (const bf16*)gate, ld_gate, (bf16*)out);                                                   \
   } while (0)
       if (kv_rank <= 128) LATENT_MMA(4);
       else if (kv_rank <= 256) LATENT_MMA(8);
@@ -1441,7 +1483,7 @@ int b200q_latent_attn(const float* qa, const void* cache, const int32_t* block_t
                                     (int)smem));                                                                   \
     latent_attn_kernel<TT, ACC><<<grid, 256, smem, as_stream(stream)>>>(                                           \
         qa, (const TT*)cache, block_table, bt_stride, row_seq, positions, heads, kv_rank, rot_dim, block_size,    \
-        window, scale, (TT*)out);                                                                                  \
+        window, scale, (const TT*)gate, ld_gate, (TT*)out);                                                        \
   } while (0)
 #define LATENT_BY_RANK(TT)                          \
   do {                                              \

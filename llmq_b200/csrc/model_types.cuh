@@ -40,6 +40,11 @@ struct b200q_layered_layer {
   // low-rank path; bonus)
   const float *shift = nullptr, *head_decay = nullptr, *temp = nullptr, *mu = nullptr, *bonus = nullptr;
   const void *inject = nullptr, *w1 = nullptr, *experts_up = nullptr;
+  // sandwich form: the norms behind the two sublayers (dynamic tanh rows [w | b | alpha], like norm1 / norm2 there),
+  // the gated GELU feed-forward (gate_up = [gate | up] rows), the per-layer token input; biases of window attention
+  const float *norm1b = nullptr, *norm2b = nullptr, *proj_b = nullptr, *o_b = nullptr, *tok_norm = nullptr;
+  const void *gate_up = nullptr, *tok_gate = nullptr, *tok_proj = nullptr;
+  float mag = 1.f;  // factor of sine and cosine (YaRN)
   std::vector<b200q_layered_layer> side;  // the mixer beside the first one (none or one)
   int64_t shift_off = 0, prev_off = 0;    // floats into a state slot: carried normed row, carried mixer input
   int64_t cache_block_off = 0;  // bytes per block of the cache regions before this layer's (own cache only)
@@ -71,6 +76,10 @@ struct b200q_layered {
   // pre-norm form: fp32 mixer input, embedding output, carried rows of a step, side mixer's output, [x | x0], blends
   float *hf = nullptr, *x0 = nullptr, *carry = nullptr;
   void *mix2 = nullptr, *cat = nullptr, *blend = nullptr;
+  // sandwich form: the second embedding table [V, n_layers * side_dim] and the token input's two small activations
+  const void* tok_embed = nullptr;
+  int64_t tok_cols = 0;
+  void *tg = nullptr, *ta = nullptr;
 };
 
 struct b200q_layer {

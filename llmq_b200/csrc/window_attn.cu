@@ -3,6 +3,9 @@
 // Rotation pairs dimension i with i + rot_dims/2 over the first rot_dims dimensions of a head (angles and their
 // sine / cosine in fp64 from position * freq[i]); the score scale and a per-head temperature are folded into the
 // fp32 query; ordinary softmax over the keys max(0, p - window + 1) .. p; one sigmoid gate number per head.
+// Options that other designs use: the first `keep_first` keys of a sequence stay visible behind the window (they are
+// visited first, as tiles of their own, then the window's keys), and scores may be soft-capped
+// (cap * tanh(score / cap)) before the softmax.
 // A scalar kernel (fp32 model, any head size) and tensor-core kernels for bf16 caches.  Scores, softmax state
 // and accumulators are fp32 in all.
 #include <stdlib.h>
@@ -63,6 +66,78 @@ __global__ void __launch_bounds__(128) window_attn_prep_kernel(const T* __restri
   for (int e = threadIdx.x; e < GV; e += blockDim.x) row[GD + e] = k[GD + e];
 }
 
+// step 1 with options: biases, an RMS norm of q and k before rotation (over the whole projection or per head), sine
+// and cosine times `mag`, a query temperature that grows with the logarithm of the position, and a layer that writes
+// no keys (it reads another layer's cache).  The token's q and k rows are staged in shared memory as fp32.
+template <typename T>
+__global__ void __launch_bounds__(128) window_attn_prep_opt_kernel(
+    const T* __restrict__ proj, int ldp, int q_off, int k_off, int v_off, const float* __restrict__ bias, int heads,
+    int kv_heads, int dim, int vdim, int qk_norm, const float* __restrict__ w_qn, const float* __restrict__ w_kn,
+    float eps, int rot_dims, const double* __restrict__ freq, float mag, const int32_t* __restrict__ positions,
+    const int32_t* __restrict__ slot_mapping, const float* __restrict__ temp, float scale, float temp_coef,
+    int temp_every, float* __restrict__ qs, T* __restrict__ cache) {
+  extern __shared__ float sh[];
+  __shared__ float red[32];
+  const int t = blockIdx.x, half = rot_dims / 2, HD = heads * dim, GD = k_off >= 0 ? kv_heads * dim : 0;
+  float* cs = sh;                 // [rot_dims/2] cos | [rot_dims/2] sin
+  float* qv = sh + rot_dims;      // [heads*dim]
+  float* kv = qv + HD;            // [kv_heads*dim]
+  const int pos = positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double sn, c;
+    sincos((double)pos * freq[i], &sn, &c);
+    cs[i] = (float)c * mag;
+    cs[half + i] = (float)sn * mag;
+  }
+  const T* pr = proj + (long long)t * ldp;
+  for (int e = threadIdx.x; e < HD; e += blockDim.x) qv[e] = ldf(pr + q_off + e) + (bias ? bias[q_off + e] : 0.f);
+  for (int e = threadIdx.x; e < GD; e += blockDim.x) kv[e] = ldf(pr + k_off + e) + (bias ? bias[k_off + e] : 0.f);
+  __syncthreads();
+  if (qk_norm == 1) {  // one norm over all heads of the projection
+    for (int which = 0; which < (GD ? 2 : 1); ++which) {
+      float* v = which ? kv : qv;
+      const float* w = which ? w_kn : w_qn;
+      const int n = which ? GD : HD;
+      float ss = 0.f;
+      for (int e = threadIdx.x; e < n; e += blockDim.x) ss = fmaf(v[e], v[e], ss);
+      const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
+      for (int e = threadIdx.x; e < n; e += blockDim.x) v[e] = v[e] * inv * w[e];
+    }
+    __syncthreads();
+  } else if (qk_norm == 2) {  // per head, one weight row shared by the heads: warp = head
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int hh = warp; hh < heads + (GD ? kv_heads : 0); hh += nw) {
+      float* v = hh < heads ? qv + hh * dim : kv + (hh - heads) * dim;
+      const float* w = hh < heads ? w_qn : w_kn;
+      float ss = 0.f;
+      for (int d = lane; d < dim; d += 32) ss = fmaf(v[d], v[d], ss);
+      const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dim + eps);
+      for (int d = lane; d < dim; d += 32) v[d] = v[d] * inv * w[d];
+    }
+    __syncthreads();
+  }
+  auto turned = [&](const float* v, int d) -> float {
+    if (d >= rot_dims) return v[d];
+    const int i = d < half ? d : d - half;
+    const float a = v[i], b = v[i + half];
+    return d < half ? a * cs[i] - b * cs[half + i] : b * cs[i] + a * cs[half + i];
+  };
+  float qmul = scale;
+  if (temp_every > 0) qmul *= (float)(1.0 + (double)temp_coef * log((double)((pos + 1) / temp_every) + 1.0));
+  for (int e = threadIdx.x; e < HD; e += blockDim.x) {
+    const int h = e / dim, d = e % dim;
+    qs[(long long)t * HD + e] = turned(qv + h * dim, d) * (qmul * (temp ? temp[h] : 1.f));
+  }
+  if (k_off < 0) return;
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  const int GV = kv_heads * vdim;
+  T* row = cache + (long long)slot * (GD + GV);
+  for (int e = threadIdx.x; e < GD; e += blockDim.x) stf(row + e, turned(kv + (e / dim) * dim, e % dim));
+  for (int e = threadIdx.x; e < GV; e += blockDim.x)
+    stf(row + GD + e, ldf(pr + v_off + e) + (bias ? bias[v_off + e] : 0.f));
+}
+
 // ------------------------------------------------------------------------------------------------
 // step 2, scalar form: one CTA per (token, key/value head, group of 8 query heads that share it).  Tiles of 32
 // cached keys and values are staged in shared memory once and used by up to 8 query heads (warp = head; lane =
@@ -75,6 +150,7 @@ __global__ void __launch_bounds__(256) window_attn_kernel(const float* __restric
                                                           const int32_t* __restrict__ row_seq,
                                                           const int32_t* __restrict__ positions, int heads, int kv_heads,
                                                           int dim, int vdim, int block_size, int window,
+                                                          int keep_first, float softcap,
                                                           const T* __restrict__ gate, int ld_gate, T* __restrict__ out) {
   extern __shared__ float sm[];
   const int KS = dim + 1, VS = vdim + 1;
@@ -99,8 +175,12 @@ __global__ void __launch_bounds__(256) window_attn_kernel(const float* __restric
 #pragma unroll
   for (int i = 0; i < ACC; ++i) acc[i] = 0.f;
   const float* qh = qsm + warp * dim;
-  for (int j0 = lo; j0 <= p; j0 += 32) {
-    const int n = min(32, p + 1 - j0);
+  // the kept first keys that the window no longer covers come first (tiles from key 0), then the window's keys
+  const int kept = min(keep_first, lo);
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  for (int phase = kept > 0 ? 0 : 1; phase < 2; ++phase)
+  for (int j0 = phase ? lo : 0, jend = phase ? p + 1 : kept; j0 < jend; j0 += 32) {
+    const int n = min(32, jend - j0);
     __syncthreads();
     for (int e = threadIdx.x; e < n * (dim + vdim); e += blockDim.x) {
       const int j = e / (dim + vdim), d = e % (dim + vdim), pos = j0 + j;
@@ -115,9 +195,9 @@ __global__ void __launch_bounds__(256) window_attn_kernel(const float* __restric
       const float* kr = ksm + lane * KS;
       float dot = 0.f;
       for (int d = 0; d < dim; ++d) dot = fmaf(qh[d], kr[d], dot);
-      s = dot;
+      s = softcap > 0.f ? softcap * tanhf(dot * inv_cap) : dot;
     }
-    const float m_new = fmaxf(m, warp_max(s));  // the tile holds at least the key j0 <= p: finite
+    const float m_new = fmaxf(m, warp_max(s));  // the tile holds at least one visible key: finite
     const float corr = expf(m - m_new);
     const float pl = lane < n ? expf(s - m_new) : 0.f;
     l = l * corr + warp_sum(pl);
@@ -156,11 +236,12 @@ __global__ void __launch_bounds__(256) window_attn_kernel(const float* __restric
 // ------------------------------------------------------------------------------------------------
 constexpr int WATT_KEYS = 64;
 constexpr float WATT_NEG = -1e30f;  // finite floor of the running maximum: exp(masked - floor) = 0, never NaN
-template <int D, int DV>
+template <int D, int DV, bool CAP>
 __global__ void __launch_bounds__(256) window_attn_mma_kernel(const float* __restrict__ qs, const bf16* __restrict__ cache,
                                                               const int32_t* __restrict__ block_table, int bt_stride,
                                                               const int32_t* __restrict__ seq_desc, int heads,
                                                               int kv_heads, int block_size, int window,
+                                                              int keep_first, float softcap,
                                                               const bf16* __restrict__ gate, int ld_gate,
                                                               bf16* __restrict__ out, int skip_single) {
   constexpr int LDK = D + 8, LDV = DV + 8;  // padded rows (bf16 elements): ldmatrix rows fall on different banks
@@ -183,10 +264,14 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(const float* __res
   const int lo_first = window > 0 ? max(0, p_first - window + 1) : 0;
   const int32_t* bt = block_table + (long long)blockIdx.x * bt_stride;
   const int GD = kv_heads * D, RS = GD + kv_heads * DV;
-  const int ntiles = (p_last - lo_first) / WATT_KEYS + 1;
+  // kept first keys that the first token's window no longer covers: whole tiles from key 0, before the window's
+  const int kept = min(keep_first, lo_first), nst = (kept + WATT_KEYS - 1) / WATT_KEYS;
+  const int ntiles = nst + (p_last - lo_first) / WATT_KEYS + 1;
+  auto tile_start = [&](int c) { return c < nst ? c * WATT_KEYS : lo_first + (c - nst) * WATT_KEYS; };
+  const float inv_cap = CAP ? 1.f / softcap : 0.f;
 
   auto load_tile = [&](int c, int buf) {
-    const int j0 = lo_first + c * WATT_KEYS;
+    const int j0 = tile_start(c);
     bf16* kb = kbuf + (long long)buf * WATT_KEYS * LDK;
     bf16* vb = vbuf + (long long)buf * WATT_KEYS * LDV;
     constexpr int CK = D / 8, CV = DV / 8, CPR = CK + CV;  // 16-byte pieces of a cached row's key and value
@@ -228,7 +313,8 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(const float* __res
   for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
   for (int c = 0; c < ntiles; ++c) {
-    const int buf = c & 1, j0 = lo_first + c * WATT_KEYS;
+    const int buf = c & 1, j0 = tile_start(c);
+    const bool sink_tile = c < nst;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();  // tile c (and, first time, the queries) is in shared memory; tile c-1 is done with
     if (c + 1 < ntiles) load_tile(c + 1, buf ^ 1);
@@ -256,7 +342,9 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(const float* __res
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int j = j0 + nt * 8 + 2 * q4 + (e & 1), r = e >> 1;
-        const float v = (j <= p_row[r] && j >= lo_row[r]) ? s[nt][e] : -INFINITY;
+        const bool see = sink_tile ? (j < kept && p_row[r] >= 0) : (j <= p_row[r] && (j >= lo_row[r] || j < keep_first));
+        const float sc = CAP ? softcap * tanhf(s[nt][e] * inv_cap) : s[nt][e];
+        const float v = see ? sc : -INFINITY;
         s[nt][e] = v;
         rmax[r] = fmaxf(rmax[r], v);
       }
@@ -334,12 +422,13 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(const float* __res
 // an SM: the kernel lives on loads in flight, not on arithmetic.
 // ------------------------------------------------------------------------------------------------
 constexpr int WDEC_WARPS = 4;
-template <int D, int DV, int WDEC_KEYS>
+template <int D, int DV, int WDEC_KEYS, bool CAP>
 __global__ void __launch_bounds__(128) window_attn_decode_mma_kernel(const float* __restrict__ qs,
                                                                      const bf16* __restrict__ cache,
                                                                      const int32_t* __restrict__ block_table,
                                                                      int bt_stride, const int32_t* __restrict__ seq_desc,
                                                                      int heads, int kv_heads, int block_size, int window,
+                                                                     int keep_first, float softcap,
                                                                      const bf16* __restrict__ gate, int ld_gate,
                                                                      bf16* __restrict__ out) {
   constexpr int LDK = D + 8, LDV = DV + 8, MS = DV + 2;
@@ -355,11 +444,14 @@ __global__ void __launch_bounds__(128) window_attn_decode_mma_kernel(const float
   const long long t = sq.row0;
   const int32_t* bt = block_table + (long long)blockIdx.x * bt_stride;
   const int GD = kv_heads * D, RS = GD + kv_heads * DV;
-  const int ntiles = (p - lo) / WDEC_KEYS + 1;
+  const int kept = min(keep_first, lo), nst = (kept + WDEC_KEYS - 1) / WDEC_KEYS;  // kept first keys: tiles of their own
+  const int ntiles = nst + (p - lo) / WDEC_KEYS + 1;
+  auto tile_start = [&](int c) { return c < nst ? c * WDEC_KEYS : lo + (c - nst) * WDEC_KEYS; };
+  const float inv_cap = CAP ? 1.f / softcap : 0.f;
   bf16* kw = kvbuf + (long long)warp * 2 * WDEC_KEYS * (LDK + LDV);
 
   auto load_tile = [&](int c, int buf) {  // by this warp alone
-    const int j0 = lo + c * WDEC_KEYS;
+    const int j0 = tile_start(c);
     bf16* kb = kw + (long long)buf * WDEC_KEYS * (LDK + LDV);
     bf16* vb = kb + WDEC_KEYS * LDK;
     constexpr int CK = D / 8, CV = DV / 8, CPR = CK + CV;
@@ -393,7 +485,7 @@ __global__ void __launch_bounds__(128) window_attn_decode_mma_kernel(const float
   for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
   for (int c = warp, it = 0; c < ntiles; c += WDEC_WARPS, ++it) {
-    const int buf = it & 1, j0 = lo + c * WDEC_KEYS;
+    const int buf = it & 1, j0 = tile_start(c), jend = c < nst ? kept : p + 1;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
     if (c + WDEC_WARPS < ntiles) load_tile(c + WDEC_WARPS, buf ^ 1);
@@ -421,7 +513,8 @@ __global__ void __launch_bounds__(128) window_attn_decode_mma_kernel(const float
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int j = j0 + nt * 8 + 2 * q4 + (e & 1), r = e >> 1;
-        const float v = (row_on[r] && j <= p) ? s[nt][e] : -INFINITY;  // tiles start at the window's first key
+        const float sc = CAP ? softcap * tanhf(s[nt][e] * inv_cap) : s[nt][e];
+        const float v = (row_on[r] && j < jend) ? sc : -INFINITY;  // tiles start at the window's first key
         s[nt][e] = v;
         rmax[r] = fmaxf(rmax[r], v);
       }
@@ -532,6 +625,36 @@ int b200q_window_attn_prep(const void* proj, int ldp, int heads, int kv_heads, i
   return B200Q_OK;
 }
 
+int b200q_window_attn_prep_ex(const void* proj, int ldp, int q_off, int k_off, int v_off, const float* bias, int heads,
+                              int kv_heads, int dim, int vdim, int qk_norm, const float* w_qn, const float* w_kn, float eps,
+                              int rot_dims, const double* freq, float mag, const int32_t* positions,
+                              const int32_t* slot_mapping, const float* temp, float scale, float temp_coef, int temp_every,
+                              float* qs, void* cache, int T_, int dtype, void* stream) {
+  const bool own = k_off >= 0;
+  B200Q_CHECK_ARG(proj && positions && qs && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && q_off >= 0 &&
+                      ldp >= q_off + heads * dim && rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim &&
+                      (rot_dims == 0 || freq) && T_ >= 0 && is_dtype(dtype) && temp_every >= 0,
+                  "window_attn_prep: bad argument (heads=%d kv_heads=%d dim=%d vdim=%d rot_dims=%d even, <= dim)", heads,
+                  kv_heads, dim, vdim, rot_dims);
+  B200Q_CHECK_ARG(!own || (slot_mapping && cache && v_off >= 0 && ldp >= k_off + kv_heads * dim &&
+                           ldp >= v_off + kv_heads * vdim),
+                  "window_attn_prep: bad key / value columns (k_off=%d v_off=%d ldp=%d)", k_off, v_off, ldp);
+  B200Q_CHECK_ARG(qk_norm >= 0 && qk_norm <= 2 && (qk_norm == 0 || (w_qn && (!own || w_kn))) && eps >= 0.f,
+                  "window_attn_prep: bad query / key norm (%d)", qk_norm);
+  if (T_ == 0) return B200Q_OK;
+  const size_t smem = (size_t)(std::max(rot_dims, 1) + heads * dim + kv_heads * dim) * sizeof(float);
+  B200Q_CHECK_ARG(smem <= 200 * 1024, "window_attn_prep: heads * dim too large for one CTA");
+  DISPATCH_T(dtype, {
+    auto kern = window_attn_prep_opt_kernel<T>;
+    if (smem > 48 * 1024) B200Q_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<T_, 128, smem, as_stream(stream)>>>((const T*)proj, ldp, q_off, k_off, v_off, bias, heads, kv_heads, dim, vdim,
+                                               qk_norm, w_qn, w_kn, eps, rot_dims, freq, mag, positions, slot_mapping,
+                                               temp, scale, temp_coef, temp_every, qs, (T*)cache);
+  });
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
 static int window_attn_mma_mode() {  // B200Q_WINDOW_ATTN_MMA=0: the scalar kernel everywhere
   static const int mode = [] {
     const char* v = getenv("B200Q_WINDOW_ATTN_MMA");
@@ -555,6 +678,17 @@ int b200q_window_attn(const float* qs, const void* cache, const int32_t* block_t
                       const int32_t* positions, const int32_t* seq_desc, int n_seqs, int T_, int heads, int kv_heads,
                       int dim, int vdim, int block_size, int window, const void* gate, int ld_gate, void* out, int dtype,
                       void* stream) {
+  return b200q_window_attn_ex(qs, cache, block_table, bt_stride, row_seq, positions, seq_desc, n_seqs, T_, heads, kv_heads,
+                              dim, vdim, block_size, window, 0, 0.f, gate, ld_gate, out, dtype, stream);
+}
+
+int b200q_window_attn_ex(const float* qs, const void* cache, const int32_t* block_table, int bt_stride,
+                         const int32_t* row_seq, const int32_t* positions, const int32_t* seq_desc, int n_seqs, int T_,
+                         int heads, int kv_heads, int dim, int vdim, int block_size, int window, int keep_first,
+                         float softcap, const void* gate, int ld_gate, void* out, int dtype, void* stream) {
+  B200Q_CHECK_ARG(keep_first >= 0 && softcap >= 0.f, "window_attn: bad kept keys (%d) or soft cap (%g)", keep_first,
+                  (double)softcap);
+  if (window <= 0) keep_first = 0;  // every earlier key is visible anyway
   B200Q_CHECK_ARG(qs && cache && block_table && row_seq && positions && out && heads > 0 && kv_heads > 0 &&
                       heads % kv_heads == 0 && dim > 0 && dim <= 512 && vdim > 0 && vdim <= 512 && block_size > 0 &&
                       window >= 0 && T_ >= 0 && is_dtype(dtype) && (!gate || ld_gate >= heads),
@@ -580,21 +714,27 @@ int b200q_window_attn(const float* qs, const void* cache, const int32_t* block_t
     dim3 dgrid(n_seqs, kv_heads);
 #define MMA_ATTN(DD, DDV)                                                                                                \
   do {                                                                                                                   \
+    if (softcap > 0.f) MMA_ATTN_C(DD, DDV, true);                                                                        \
+    else MMA_ATTN_C(DD, DDV, false);                                                                                     \
+  } while (0)
+#define MMA_ATTN_C(DD, DDV, CC)                                                                                              \
+  do {                                                                                                                   \
     if (tiles) {                                                                                                         \
       if (msm > 48 * 1024)                                                                                               \
-        B200Q_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<DD, DDV>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+        B200Q_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<DD, DDV, CC>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
                                         (int)msm));                                                                      \
-      window_attn_mma_kernel<DD, DDV><<<mgrid, nw * 32, msm, st>>>(qs, (const bf16*)cache, block_table, bt_stride,       \
+      window_attn_mma_kernel<DD, DDV, CC><<<mgrid, nw * 32, msm, st>>>(qs, (const bf16*)cache, block_table, bt_stride,       \
                                                                    seq_desc, heads, kv_heads, block_size, window,        \
+                                                                   keep_first, softcap,                                  \
                                                                    (const bf16*)gate, ld_gate, (bf16*)out, dec ? 1 : 0); \
       B200Q_LAUNCH_CHECK();                                                                                              \
     }                                                                                                                    \
     if (dec) {                                                                                                           \
-      auto dk = dkeys == 16 ? window_attn_decode_mma_kernel<DD, DDV, 16> : window_attn_decode_mma_kernel<DD, DDV, 32>;   \
+      auto dk = dkeys == 16 ? window_attn_decode_mma_kernel<DD, DDV, 16, CC> : window_attn_decode_mma_kernel<DD, DDV, 32, CC>;   \
       if (dsm > 48 * 1024)                                                                                               \
         B200Q_CUDA(cudaFuncSetAttribute(dk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm));                     \
       dk<<<dgrid, 128, dsm, st>>>(qs, (const bf16*)cache, block_table, bt_stride, seq_desc, heads, kv_heads, block_size, \
-                                  window, (const bf16*)gate, ld_gate, (bf16*)out);                                       \
+                                  window, keep_first, softcap, (const bf16*)gate, ld_gate, (bf16*)out);                  \
       B200Q_LAUNCH_CHECK();                                                                                              \
     }                                                                                                                    \
   } while (0)
@@ -603,6 +743,7 @@ int b200q_window_attn(const float* qs, const void* cache, const int32_t* block_t
     else if (vdim == 64) MMA_ATTN(128, 64);
     else MMA_ATTN(128, 128);
 #undef MMA_ATTN
+#undef MMA_ATTN_C
     return B200Q_OK;
   }
   dim3 grid(T_, kv_heads, (rep + 7) / 8);
@@ -614,7 +755,7 @@ int b200q_window_attn(const float* qs, const void* cache, const int32_t* block_t
       auto kern = window_attn_kernel<T, ACC>;                                                                             \
       if (smem > 48 * 1024) B200Q_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
       kern<<<grid, 256, smem, st>>>(qs, (const T*)cache, block_table, bt_stride, row_seq, positions, heads, kv_heads, dim, \
-                                    vdim, block_size, window, (const T*)gate, ld_gate, (T*)out);                          \
+                                    vdim, block_size, window, keep_first, softcap, (const T*)gate, ld_gate, (T*)out);      \
     });                                                                                                                   \
   } while (0)
   if (vdim <= 64) SCALAR(2);

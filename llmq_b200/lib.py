@@ -57,6 +57,11 @@ class ModelConfig(C.Structure):
         ("learned_pos", C.c_int32),
         ("token_shift", C.c_int32),
         ("logit_softcap", C.c_float),
+        # sandwich form
+        ("norm_kind", C.c_int32),
+        ("residual_mult", C.c_float),
+        ("side_dim", C.c_int32),
+        ("logit_scale", C.c_float),
     ]
 
 
@@ -65,9 +70,15 @@ ARCH_GEMMA2 = 1
 ARCH_RAMOPEL = 2
 ARCH_NORIDRA = 3
 ARCH_PALUZEN = 4
+ARCH_KABAVIK = 5
 FORM_PARALLEL = 0
 FORM_POSTNORM = 1
 FORM_PRENORM = 2
+FORM_SANDWICH = 3
+NORM_RMS = 0
+NORM_DYT = 1
+NORM_CAST = 2
+NORM_NONE = 3
 DTYPE_BF16 = 0
 DTYPE_F32 = 1
 MIXER_LATENT_ATTN = 1
@@ -84,6 +95,7 @@ FF_MOE = 2
 FF_MOE_SIGMOID = 3
 FF_RELU2 = 4
 FF_MOE_GROUPED = 5
+FF_GEGLU = 6
 
 
 class LayerDesc(C.Structure):
@@ -98,6 +110,9 @@ class LayerDesc(C.Structure):
         ("inject", C.c_int32), ("mix_scale", C.c_float), ("n_identity", C.c_int32), ("n_groups", C.c_int32),
         ("keep_groups", C.c_int32), ("side_mixer", C.c_int32), ("side_heads", C.c_int32), ("side_dim", C.c_int32),
         ("side_vdim", C.c_int32), ("side_decay_rank", C.c_int32), ("side_scale", C.c_float),
+        ("keep_first", C.c_int32), ("qk_norm", C.c_int32), ("proj_bias", C.c_int32), ("bare", C.c_int32),
+        ("head_gate", C.c_int32), ("q_temp_coef", C.c_float), ("q_temp_every", C.c_int32),
+        ("rot_factor", C.c_double), ("rot_original", C.c_double), ("rot_fast", C.c_double), ("rot_slow", C.c_double),
     ]
 
 
@@ -248,6 +263,20 @@ SIGNATURES = {
     "b200q_softcap_f32": (_i, [_vp, _i64, _f, _vp]),
     "b200q_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "b200q_copy_f32": (_i, [_vp, _vp, _i64, _vp]),
+    # sandwich layers, options of window / latent attention
+    "b200q_rot_frequencies": (_i, [_i, C.c_double, C.c_double, C.c_double, C.c_double, C.c_double, _vp, _vp]),
+    "b200q_row_norm": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "b200q_sandwich_add": (_i, [_vp, _vp, _vp, _i, _vp, _f, _i, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "b200q_scale_f32": (_i, [_vp, _i64, _f, _vp]),
+    "b200q_gelu_glu": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
+    "b200q_token_side_gate": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _vp]),
+    "b200q_window_attn_prep_ex": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _f, _i, _vp, _f, _vp, _vp,
+                                       _vp, _f, _f, _i, _vp, _vp, _i, _i, _vp]),
+    "b200q_window_attn_ex": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _vp,
+                                  _i, _vp]),
+    "b200q_latent_prep_ex": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "b200q_rope_pairs_q_ex": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp]),
+    "b200q_latent_attn_ex": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp]),
     "b200q_model_create_layered": (_i, [C.POINTER(ModelConfig), C.POINTER(LayerDesc), C.POINTER(_vp)]),
     "b200q_model_kv_block_bytes": (_i64, [_vp]),
     "b200q_model_state_slot_bytes": (_i64, [_vp]),

@@ -17,7 +17,7 @@ from typing import Dict, Iterable, List, Optional, Tuple
 import torch
 
 from . import lib as L
-from . import noridra, paluzen, ramopel
+from . import kabavik, noridra, paluzen, ramopel
 
 BLOCK_SIZE = 16
 
@@ -189,10 +189,10 @@ GEMMA_2_2B = ModelSpec(hidden=2304, n_layers=26, n_q_heads=8, n_kv_heads=4, head
                        attn_softcap=50.0, final_softcap=30.0, sliding_window=4096)
 BUILTIN_SPECS = {"llama-3-8b": LLAMA_3_8B, "llama-3.2-1b": LLAMA_32_1B,
                  "gemma-2-9b": GEMMA_2_9B, "gemma-2-2b": GEMMA_2_2B, **ramopel.BUILTIN_SPECS,
-                 **noridra.BUILTIN_SPECS, **paluzen.BUILTIN_SPECS}
+                 **noridra.BUILTIN_SPECS, **paluzen.BUILTIN_SPECS, **kabavik.BUILTIN_SPECS}
 # config.json "architecture" -> the module that reads it (layered designs; HF-style configs carry "architectures")
 LAYERED_DESIGNS = {ramopel.ARCHITECTURE: ramopel.RamopelSpec, noridra.ARCHITECTURE: noridra.NoridraSpec,
-                   paluzen.ARCHITECTURE: paluzen.PaluzenSpec}
+                   paluzen.ARCHITECTURE: paluzen.PaluzenSpec, kabavik.ARCHITECTURE: kabavik.KabavikSpec}
 
 
 def rope_table(max_pos: int, head_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
@@ -395,7 +395,7 @@ class NativeModel:
         torch.cuda.synchronize(self.device)
 
     def _init_layered(self, weights, max_tokens, max_seqs, num_blocks, gpu_memory_utilization, max_logit_rows):
-        """a layered architecture (Ramopel, Noridra, Paluzen): one b200q_layer_desc per layer, a paged cache for the
+        """a layered architecture (Ramopel, Noridra, Paluzen, Kabavik): one b200q_layer_desc per layer, a paged cache for the
         attention layers that own one, and one fp32 state slot per live sequence (recurrent states and the
         carried inputs of convolutions)"""
         spec, lib = self.spec, self.lib
