@@ -342,7 +342,8 @@ def save_checkpoint(path: str, sd: Dict[str, torch.Tensor]) -> None:
     names = {v: k for k, v in _ST_DTYPES.items()}
     header, blobs, at = {}, [], 0
     for k, t in sd.items():
-        b = t.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        # a tensor without axes (one scalar) is written through a one-element view and keeps its empty shape
+        b = t.detach().cpu().contiguous().reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[k] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(b)]}
         blobs.append(b)
         at += len(b)
