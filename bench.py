@@ -697,7 +697,12 @@ def run_compare(args):
         cache = state = 0
         for ly in spec.layers:
             kind = getattr(ly, "kind", None)        # Paluzen's layer runs (a repeated layer counts once per pass)
-            if kind == "lightning":
+            if kind in ("attention", "attention_2") and hasattr(ly, "keep_first"):   # Kabavik: window + kept first keys
+                seen = min(C0 + 1, ly.window + ly.keep_first) if ly.window else C0 + 1
+                cache += B * seen * ly.kv_heads * (ly.dim + ly.vdim) * 2
+            elif kind == "latent_attention":
+                cache += B * min(C0 + 1, ly.window or C0 + 1) * (ly.kv_rank + ly.rot_dim) * 2
+            elif kind == "lightning":
                 state += B * ly.heads * ly.dim * ly.vdim * 4 * 2
             elif kind == "parallel":
                 cache += B * min(C0 + 1, ly.window or C0 + 1) * ly.kv_heads * (ly.dim + ly.vdim) * 2
@@ -714,14 +719,33 @@ def run_compare(args):
                 state += B * ly.inner * ly.state * 4 * 2
         return cache, state
 
+    def prefill_attention_flops(spec):
+        """score and value products of the cache-reading attention layers over the prefill workload (Kabavik's three
+        mixers, Paluzen's window attention)"""
+        fl = 0.0
+        for ly in spec.layers:
+            kind = getattr(ly, "kind", None)
+            if kind in ("attention", "attention_2", "parallel"):
+                per_key = 2.0 * ly.heads * (ly.dim + ly.vdim)
+            elif kind == "latent_attention" and hasattr(ly, "keep_first"):
+                per_key = 2.0 * ly.heads * (2 * ly.kv_rank + ly.rot_dim)
+            else:
+                continue
+            w = ly.window or S_p
+            keys = sum(min(p + 1, w) for p in range(S_p)) + getattr(ly, "keep_first", 0) * max(S_p - w, 0)
+            fl += per_key * keys * n_p
+        return fl
+
     frac = lambda by, ms: round(by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3) if ms > 0 else None
     tf = lambda fl, ms: round(fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 3) if ms > 0 else None
     results = {}
-    if args.compare in ("noridra", "paluzen"):
+    if args.compare in ("noridra", "paluzen", "kabavik"):
         # the design beside the closest existing one at equal width and layer count: Noridra beside Ramopel
         # (layered, recurrent state slots, routed experts); Paluzen beside Noridra (windowed / chunked grouped-query
         # attention on the tensor cores, decayed outer-product states, routed experts)
-        new, old = args.compare, {"noridra": "ramopel", "paluzen": "noridra"}[args.compare]
+        # Kabavik beside Paluzen (grouped-query window attention on the tensor cores, fp32 residual with fused sums and
+        # norms, gated feed-forwards through the same GEMM)
+        new, old = args.compare, {"noridra": "ramopel", "paluzen": "noridra", "kabavik": "paluzen"}[args.compare]
         for key in (args.compare_sizes or f"{new}-1b,{new}-3b").split(","):
             nspec, rspec = BUILTIN_SPECS[key], BUILTIN_SPECS[key.replace(new, old)]
             n, r = measure(nspec), measure(rspec)
@@ -734,6 +758,8 @@ def run_compare(args):
                               "decode_attention_of_hbm": frac(cache, k["decode_attn"]),
                               "decode_recurrence_of_hbm": frac(state, k["prefill_attn"]),
                               "prefill_gemm_of_cublas": tf(pf, m["prefill"]["kernel_ms_per_run"]["gemm"]),
+                              "prefill_attention_of_cublas": tf(prefill_attention_flops(spec),
+                                                                m["prefill"]["kernel_ms_per_run"]["decode_attn"]),
                               "decode_cache_mb": round(cache / 1e6, 2), "decode_state_mb": round(state / 1e6, 2)}
             results[key] = {new: n, old + "_equal_size": r,
                             "matrix_gb_per_token": {new: round(nspec.weight_bytes_per_token() / 1e9, 3),
@@ -744,7 +770,9 @@ def run_compare(args):
                                                        "decode": f"{B} sequences at context {C0}"},
                           "units": "decode_*_of_hbm: fraction of the measured HBM copy bandwidth (bytes a step must move / "
                                    "device time of the kernel category; recurrence = delta rules and scans, attention = "
-                                   "cache readers); prefill_gemm_of_cublas: matrix flops / gemm time over measured cuBLAS bf16",
+                                   "cache readers); prefill_gemm_of_cublas: matrix flops / gemm time over measured cuBLAS bf16; "
+                                   "prefill_attention_of_cublas: score and value flops of the cache-reading attention layers "
+                                   "/ their time over the same peak",
                           "results": results}))
         return
     for key in (args.compare_sizes or "ramopel-1b,ramopel-3b").split(","):
@@ -809,9 +837,10 @@ def main():
     ap.add_argument("--cpu-budget-s", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dry-run", action="store_true", help="host-logic self-test without a GPU (not a measurement)")
-    ap.add_argument("--compare", default=None, choices=["ramopel", "noridra", "paluzen"],
+    ap.add_argument("--compare", default=None, choices=["ramopel", "noridra", "paluzen", "kabavik"],
                     help="instead of the headline workload: prefill / decode throughput of this design beside the closest "
-                         "existing model of equal size (ramopel: a Llama decoder; noridra: Ramopel), random weights, one "
+                         "existing model of equal size (ramopel: a Llama decoder; noridra: Ramopel; paluzen: Noridra; kabavik: Paluzen), random "
+                         "weights, one "
                          "JSON line")
     ap.add_argument("--compare-sizes", default=None, help="builtin sizes, default <design>-1b,<design>-3b")
     ap.add_argument("--compare-prompt", type=int, default=2048)
