@@ -475,6 +475,9 @@ int b200q_sandwich_add(float* x_dev, const void* y_dev, const float* bias_dev, i
 int b200q_scale_f32(float* v_dev, int64_t n, float a, void* stream);
 /* gated unit: gate_up row = [g (F) | u (F)]; y = gelu_tanh(g) * u */
 int b200q_gelu_glu(const void* gate_up_dev, void* y_dev, int64_t rows, int F, int dtype, void* stream);
+/* the same over rows whose gate and up values are interleaved in blocks of `block` columns ([g | u | g | u ...], the
+ * layout of b200q_gemm_geglu_bf16's weight rows; block 0 = [g (F) | u (F)]; block must divide F) */
+int b200q_gelu_glu_ex(const void* gate_up_dev, void* y_dev, int64_t rows, int F, int block, int dtype, void* stream);
 /* per-layer token input: out[t, j] = gelu_tanh(g[t, j]) * table[id(t), col0 + j], j < D (ids < 0 as in b200q_embed_ex;
  * g rows of stride ldg, table rows of stride ld_table, both in the model dtype) */
 int b200q_token_side_gate(const void* g_dev, int ldg, const int32_t* ids_dev, const int32_t* prev_out_dev,
@@ -635,7 +638,9 @@ typedef struct b200q_model_config {
  * score = its largest choice score); weights = the chosen scores without correction, divided by their sum.  The
  * last `n_identity` router outputs are identity experts: they return their input.                               */
 #define B200Q_FF_MOE_GROUPED 5
-#define B200Q_FF_GEGLU 6            /* down(gelu_tanh(gate h) * up h); "mlp.gate_up" [2*ff, W] = gate rows, then up rows */
+#define B200Q_FF_GEGLU 6            /* down(gelu_tanh(gate h) * up h); "mlp.gate_up" [2*ff, W] = gate rows, then up rows,
+                                       or "mlp.gate_up_il" = the same rows interleaved in blocks of 128 (ff a multiple
+                                       of 128), which a bf16 model runs with the unit in the product's epilogue */
 
 typedef struct b200q_layer_desc {
   int32_t mixer;        /* B200Q_MIXER_*                                                               */

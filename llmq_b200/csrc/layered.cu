@@ -637,6 +637,14 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
   }
   if (d.ff == B200Q_FF_GEGLU) {
     FIELD("mlp.gate_up", l.gate_up, 2 * (int64_t)d.ff_dim, W)
+    if (!strcmp(field, "mlp.gate_up_il")) {
+      B200Q_CHECK_ARG(d.ff_dim % 128 == 0, "layer %d: interleaved gate / up rows need ff (%d) to be a multiple of 128", li,
+                      d.ff_dim);
+      if ((rc = expect(2 * (int64_t)d.ff_dim, W))) return rc;
+      l.gate_up = p;
+      l.gate_up_il = true;
+      return B200Q_OK;
+    }
     FIELD("mlp.down", l.ff_down, W, d.ff_dim)
   } else if (d.ff == B200Q_FF_RELU2) {
     FIELD("mlp.up", l.up, d.ff_dim, W)
@@ -1068,8 +1076,16 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
         const int F = d.ff_dim;
         TRY(EW, (double)T * W * (8 + 2 * es),
             b200q_sandwich_add(y->x, y->mix, o_b, NK, l.norm1b, mult, NK, l.norm2, y->h2, T, W, c.rms_eps, dt, stream));
-        LIN(y->h2, W, l.gate_up, nullptr, y->ffh, 2 * F, 2 * F, W, 0);  // [gate | up]
-        TRY(EW, 3.0 * T * F * es, b200q_gelu_glu(y->ffh, y->ffa, T, F, dt, stream));
+        // (steps of few tokens keep the plain product: its 128-wide tiles put twice as many SMs on the weight stream)
+        if (l.gate_up_il && dt == B200Q_DTYPE_BF16 && W % 64 == 0 && T >= 512 &&
+            ((reinterpret_cast<uintptr_t>(y->h2) | reinterpret_cast<uintptr_t>(l.gate_up) |
+              reinterpret_cast<uintptr_t>(y->ffa)) & 15) == 0) {
+          // the gated unit in the product's epilogue: the [T, 2F] activations are never written
+          TRY(B200Q_PROF_GEMM, 2.0 * T * 2.0 * F * W, b200q_gemm_geglu_bf16(y->h2, l.gate_up, y->ffa, T, 2 * F, W, stream));
+        } else {
+          LIN(y->h2, W, l.gate_up, nullptr, y->ffh, 2 * F, 2 * F, W, 0);  // [gate | up], or blocks of 128 of each
+          TRY(EW, 3.0 * T * F * es, b200q_gelu_glu_ex(y->ffh, y->ffa, T, F, l.gate_up_il ? 128 : 0, dt, stream));
+        }
         LIN(y->ffa, F, l.ff_down, nullptr, y->ffo, W, W, F, 0);
         TRY(EW, (double)T * W * (8 + 2 * es),
             b200q_sandwich_add(y->x, y->ffo, nullptr, NK, l.norm2b, mult, after_kind, after_w, y->h1, T, W, c.rms_eps, dt,

@@ -45,6 +45,7 @@ struct b200q_layered_layer {
   const float *norm1b = nullptr, *norm2b = nullptr, *proj_b = nullptr, *o_b = nullptr, *tok_norm = nullptr;
   const void *gate_up = nullptr, *tok_gate = nullptr, *tok_proj = nullptr;
   float mag = 1.f;  // factor of sine and cosine (YaRN)
+  bool gate_up_il = false;  // gate_up rows interleaved in blocks of 128 (the fused product + gated unit's layout)
   std::vector<b200q_layered_layer> side;  // the mixer beside the first one (none or one)
   int64_t shift_off = 0, prev_off = 0;    // floats into a state slot: carried normed row, carried mixer input
   int64_t cache_block_off = 0;  // bytes per block of the cache regions before this layer's (own cache only)

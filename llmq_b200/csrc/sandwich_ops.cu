@@ -137,26 +137,41 @@ __global__ void __launch_bounds__(256) sandwich_add_kernel(float* __restrict__ x
   }
 }
 
+// where column c's gate and up values lie in a [2F] row: block 0 = [g (F) | u (F)]; block b > 0 = gate and up
+// interleaved in blocks of b columns ([g b | u b | g b | u b ...])
+__device__ __forceinline__ void glu_columns(int c, int F, int block, int& g_at, int& u_at) {
+  if (block > 0) {
+    g_at = (c / block) * 2 * block + c % block;
+    u_at = g_at + block;
+  } else {
+    g_at = c;
+    u_at = F + c;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) gelu_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows,
-                                                       int F) {
+                                                       int F, int block) {
   const long long total = rows * F;
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
        e += (long long)gridDim.x * blockDim.x) {
     const long long r = e / F;
-    const int c = (int)(e % F);
-    stf(y + e, gelu_tanhf_(ldf(gu + r * 2 * F + c)) * ldf(gu + r * 2 * F + F + c));
+    int g_at, u_at;
+    glu_columns((int)(e % F), F, block, g_at, u_at);
+    stf(y + e, gelu_tanhf_(ldf(gu + r * 2 * F + g_at)) * ldf(gu + r * 2 * F + u_at));
   }
 }
 __global__ void __launch_bounds__(256) gelu_glu_v8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ y,
-                                                          long long rows, int F) {
+                                                          long long rows, int F, int block) {
   const int per = F / 8;
   const long long total = rows * per;
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
        e += (long long)gridDim.x * blockDim.x) {
     const long long r = e / per;
     const int c = (int)(e % per) * 8;
-    const uint4 g = ld_v4(gu + r * 2 * F + c), u = ld_v4(gu + r * 2 * F + F + c);
+    int g_at, u_at;
+    glu_columns(c, F, block, g_at, u_at);  // block is a multiple of 8: the eight columns stay together
+    const uint4 g = ld_v4(gu + r * 2 * F + g_at), u = ld_v4(gu + r * 2 * F + u_at);
     const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
     uint32_t o[4];
 #pragma unroll
@@ -258,16 +273,22 @@ int b200q_sandwich_add(float* x, const void* y, const float* bias, int post_kind
 }
 
 int b200q_gelu_glu(const void* gate_up, void* y, int64_t rows, int F, int dtype, void* stream) {
-  B200Q_CHECK_ARG(gate_up && y && rows >= 0 && F > 0 && is_dtype(dtype), "gelu_glu: bad argument");
+  return b200q_gelu_glu_ex(gate_up, y, rows, F, 0, dtype, stream);
+}
+
+int b200q_gelu_glu_ex(const void* gate_up, void* y, int64_t rows, int F, int block, int dtype, void* stream) {
+  B200Q_CHECK_ARG(gate_up && y && rows >= 0 && F > 0 && is_dtype(dtype) && block >= 0 && (block == 0 || F % block == 0),
+                  "gelu_glu: bad argument (F=%d, blocks of %d)", F, block);
   if (rows == 0) return B200Q_OK;
-  if (dtype == B200Q_DTYPE_BF16 && F % 8 == 0 &&
+  if (dtype == B200Q_DTYPE_BF16 && F % 8 == 0 && block % 8 == 0 &&
       ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
-    gelu_glu_v8_kernel<<<grid_for(rows * (F / 8)), 256, 0, as_stream(stream)>>>((const bf16*)gate_up, (bf16*)y, rows, F);
+    gelu_glu_v8_kernel<<<grid_for(rows * (F / 8)), 256, 0, as_stream(stream)>>>((const bf16*)gate_up, (bf16*)y, rows, F,
+                                                                               block);
     B200Q_LAUNCH_CHECK();
     return B200Q_OK;
   }
   DISPATCH_T(dtype, (gelu_glu_kernel<T><<<grid_for(rows * F), 256, 0, as_stream(stream)>>>((const T*)gate_up, (T*)y,
-                                                                                         rows, F)));
+                                                                                         rows, F, block)));
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

@@ -243,6 +243,17 @@ def _pad_rows(t: torch.Tensor, mult: int = 64) -> torch.Tensor:
     return torch.cat([t, t.new_zeros((pad,) + tuple(t.shape[1:]))], 0) if pad else t
 
 
+GLU_BLOCK = 128
+
+
+def _interleave(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[F, W], [F, W] -> [2F, W] with rows [256j, 256j + 128) = gate rows [128j, 128j + 128) and the next 128 the same
+    rows of up: one 256-wide tile of the product carries both halves of 128 outputs, so the gated unit can be applied
+    in the product's epilogue"""
+    F, W = gate.shape
+    return torch.stack([gate.view(F // GLU_BLOCK, GLU_BLOCK, W), up.view(F // GLU_BLOCK, GLU_BLOCK, W)], 1).reshape(2 * F, W)
+
+
 def _dyt_row(sd, name: str) -> torch.Tensor:
     """a dynamic-tanh norm as the engine binds it: one row [w | b | alpha]"""
     return torch.cat([sd[name].reshape(-1).float(), sd[name + ".b"].reshape(-1).float(),
@@ -254,7 +265,7 @@ def engine_weights(spec: KabavikSpec, sd: Dict[str, torch.Tensor]) -> Iterable[T
     1-D results are vectors and constants (bound as fp32 rows).  Fusions: the projections that read a mixer's input
     become one matrix with zero rows up to a multiple of 64 (attention: q, k, v — q alone when the keys and values
     are an earlier layer's; latent attention: q, the latent, the shared rotated key, the gate rows), their biases one
-    row; gate and up of the feed-forward are stacked; each head's key up-projection is stored transposed (the engine
+    row; gate and up of the feed-forward are stacked (interleaved in blocks of 128 rows when ff is a multiple of 128); each head's key up-projection is stored transposed (the engine
     carries the query into the latent space instead of expanding every cached latent into keys); a dynamic-tanh
     norm is one row [w | b | alpha]."""
     yield "embed", sd["embed"]
@@ -287,7 +298,10 @@ def engine_weights(spec: KabavikSpec, sd: Dict[str, torch.Tensor]) -> Iterable[T
             f = p + "mlp."
             yield o + "norm2", _dyt_row(sd, p + "norm2")
             yield o + "norm2b", _dyt_row(sd, p + "norm2b")
-            yield o + "mlp.gate_up", torch.cat([sd[f + "gate"], sd[f + "up"]], 0)
+            if ly.ff_dim % GLU_BLOCK == 0:
+                yield o + "mlp.gate_up_il", _interleave(sd[f + "gate"], sd[f + "up"])
+            else:
+                yield o + "mlp.gate_up", torch.cat([sd[f + "gate"], sd[f + "up"]], 0)
             yield o + "mlp.down", sd[f + "down"]
         if spec.side_dim:
             yield o + "tok.gate", sd[p + "side.gate"]

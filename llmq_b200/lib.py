@@ -269,6 +269,7 @@ SIGNATURES = {
     "b200q_sandwich_add": (_i, [_vp, _vp, _vp, _i, _vp, _f, _i, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200q_scale_f32": (_i, [_vp, _i64, _f, _vp]),
     "b200q_gelu_glu": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
+    "b200q_gelu_glu_ex": (_i, [_vp, _vp, _i64, _i, _i, _i, _vp]),
     "b200q_token_side_gate": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _vp]),
     "b200q_window_attn_prep_ex": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _f, _i, _vp, _f, _vp, _vp,
                                        _vp, _f, _f, _i, _vp, _vp, _i, _i, _vp]),

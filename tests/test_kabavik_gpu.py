@@ -71,6 +71,7 @@ ONE_LAYER = {
     "attention_2_no_temperature_tight_cap": [attn2(heads=2, kv_heads=1, dim=24, vdim=40, softcap=0.5, every=0)],
     "attention_2_tile_sizes": [attn2(heads=4, kv_heads=1, dim=64, vdim=128, softcap=3.0, every=5)],
     "dense_and_token_input": [attn2(heads=1, kv_heads=1, dim=8, vdim=8, **DENSE)],
+    "dense_gate_and_up_in_blocks": [attn2(heads=1, kv_heads=1, dim=8, vdim=8, ff="dense", ff_dim=256)],
 }
 
 
@@ -275,6 +276,17 @@ def test_sums_norms_and_gated_units(cuda):
             L.check(lib.b200q_gelu_glu(gud.data_ptr(), out.data_ptr(), T, F, dtype, None))
             torch.cuda.synchronize()
             assert float((out.cpu().double() - O.gelu_tanh(gu[:, :F].double()) * gu[:, F:].double()).abs().max()) < tol * 4
+            # gate and up interleaved in blocks of 8 columns
+            FB = 48
+            gb = torch.randn(T, 2 * FB, generator=g).to(tdt)
+            out = torch.zeros(T, FB, dtype=tdt, device=cuda)
+            gbd = gb.to(cuda)
+            L.check(lib.b200q_gelu_glu_ex(gbd.data_ptr(), out.data_ptr(), T, FB, 8, dtype, None))
+            torch.cuda.synchronize()
+            blocks = gb.double().view(T, FB // 8, 2, 8)
+            want = (O.gelu_tanh(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(T, FB)
+            assert float((out.cpu().double() - want).abs().max()) < tol * 4
+            assert lib.b200q_gelu_glu_ex(gbd.data_ptr(), out.data_ptr(), T, FB, 5, dtype, None) != 0
             # the per-layer token input's gate: columns 5 .. 5 + D of the token's table row; an id below zero names
             # a token that the step before sampled
             D, V = 6, 11
@@ -550,6 +562,26 @@ def test_other_sizes_power_of_two_everything(cuda):
         model, eng = build(spec, sd, dtype)
         got = replay_cut(eng, 1, toks, [130, 2, 9])
         check_close(got, want, dtype)
+        eng.close()
+        model.close()
+
+
+def test_long_portions_take_the_product_with_the_gated_unit_in_its_epilogue(cuda):
+    """portions of 512 tokens and more run gate / up through the fused product (bf16, sizes in blocks of 128), shorter
+    ones through the plain product and the elementwise kernel over the same interleaved rows: one prompt whole, cut
+    in two long portions, and cut short"""
+    layers = [attn(heads=2, kv_heads=1, dim=64, vdim=64, window=200, keep_first=3, rot_dims=32, ff="dense", ff_dim=256),
+              latent(heads=2, dim=32, rot_dim=32, vdim=64, kv_rank=64, window=300, ff="dense", ff_dim=128)]
+    spec = small_spec(width=128, vocab=256, layers=layers, side_dim=8)
+    sd = checkpoint(spec, seed=9)
+    toks = tokens(1100, spec.vocab, 4)
+    want = oracle_logits(spec, sd, toks)
+    for dtype in (torch.float32, torch.bfloat16):
+        model, eng = build(spec, sd, dtype, max_tokens=1152)
+        for rid, cuts in ((1, [1100]), (2, [520, 580]), (3, [300, 511, 289])):
+            got = replay_cut(eng, rid, toks, cuts)
+            eng.abort(rid)
+            check_close(got, want, dtype, str(cuts))
         eng.close()
         model.close()
 

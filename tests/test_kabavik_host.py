@@ -126,6 +126,14 @@ def test_engine_weights_shapes_and_fusions():
     assert torch.equal(ukt[l1.kv_rank:2 * l1.kv_rank].T, sd["l1.mix.uk"][l1.dim:2 * l1.dim])
     gu = ew["layers.0.mlp.gate_up"]
     assert gu.shape == (2 * 72, W) and torch.equal(gu[72:], sd["l0.mlp.up"])
+    # a feed-forward whose size is a multiple of 128: gate and up rows alternate in blocks of 128
+    sp2 = small_spec(layers=[attn2(ff="dense", ff_dim=256)], side_dim=0)
+    sd2 = checkpoint(sp2, 4)
+    ew2 = dict(sp2.engine_weights(sd2))
+    il = ew2["layers.0.mlp.gate_up_il"]
+    assert "layers.0.mlp.gate_up" not in ew2 and il.shape == (512, W)
+    assert torch.equal(il[:128], sd2["l0.mlp.gate"][:128]) and torch.equal(il[128:256], sd2["l0.mlp.up"][:128])
+    assert torch.equal(il[256:384], sd2["l0.mlp.gate"][128:]) and torch.equal(il[384:], sd2["l0.mlp.up"][128:])
     assert spec.weight_bytes_per_token() > 0
 
 
