@@ -139,9 +139,9 @@ def test_engine_weights_shapes_and_fusions():
 
 def test_rotation_frequencies_match_the_plain_form():
     lib = L.load()
-    cases = [dict(dims=16, base=10000.0), dict(dims=24, base=250000.0, scaling={"factor": 2.0}),
+    cases = [dict(dims=12, base=5000.0), dict(dims=20, base=80000.0, scaling={"factor": 2.5}),
              dict(dims=8, base=100.0, scaling={"factor": 3.0, "original": 64.0, "fast": 8.0, "slow": 1.0}),
-             dict(dims=64, base=10000.0, scaling={"factor": 4.0, "original": 4096.0, "fast": 32.0, "slow": 1.0}),
+             dict(dims=64, base=20000.0, scaling={"factor": 4.0, "original": 4096.0, "fast": 16.0, "slow": 2.0}),
              dict(dims=6, base=50.0, scaling={"factor": 1.5, "original": 16.0, "fast": 1.0, "slow": 1.0})]  # lo == hi
     for rot in cases:
         sc = rot.get("scaling") or {}
