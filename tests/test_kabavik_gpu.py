@@ -499,17 +499,28 @@ def test_long_decoding_past_windows_pages_and_temperature_steps(cuda, small):
         model.close()
 
 
-def test_mixed_batches_pages_reused(cuda, small):
+def _tile_spec():
+    """head sizes and latents the tensor-core attention kernels take, with kept keys, a cap, borrowed keys"""
+    layers = [attn(heads=4, kv_heads=2, dim=64, vdim=64, window=24, keep_first=3, rot_dims=32, ff="dense", ff_dim=128),
+              latent(heads=3, dim=32, rot_dim=64, vdim=32, kv_rank=64, window=20, ff="dense", ff_dim=64),
+              attn2(heads=2, kv_heads=1, dim=128, vdim=64, softcap=5.0, every=16, ff="dense", ff_dim=64),
+              attn(heads=8, kv_heads=2, dim=64, vdim=64, window=17, keep_first=20, rot_dims=32, kv_from=0)]
+    return small_spec(width=128, vocab=256, layers=layers, side_dim=8)
+
+
+@pytest.mark.parametrize("which,dtype", [("small", torch.float32), ("tiles", torch.float32), ("tiles", torch.bfloat16)])
+def test_mixed_batches_pages_reused(cuda, small, which, dtype):
     """up to three live requests in a pool too small for all of them: portions of some beside single tokens of
     others, requests that sit a step out, finished requests whose pages go to the next one (the pool starts
     dirty).  Every request must come out as if it had run alone."""
-    spec, sd = small
+    spec, sd = small if which == "small" else (_tile_spec(), None)
+    sd = sd or checkpoint(spec, seed=31)
     rng = np.random.default_rng(7)
     lens = [37, 5, 64, 18, 1, 49, 33, 2, 80]
     reqs = {i: tokens(n, spec.vocab, 100 + i) for i, n in enumerate(lens)}
     want = {i: oracle_logits(spec, sd, t) for i, t in reqs.items()}
-    model, eng = build(spec, sd, max_tokens=160, max_seqs=3, num_blocks=13)   # 208 token places for 289 tokens
-    model.kv.view(torch.float32).fill_(1e3)
+    model, eng = build(spec, sd, dtype, max_tokens=160, max_seqs=3, num_blocks=13)   # 208 token places for 289 tokens
+    model.kv.view(torch.int16).fill_(0x4E4E)                                  # large values in either dtype
     got = {i: [] for i in reqs}
     at = {i: 0 for i in reqs}
     waiting, live = list(reqs), []
@@ -540,7 +551,7 @@ def test_mixed_batches_pages_reused(cuda, small):
             eng.abort(i)
             live.remove(i)
     for i in reqs:
-        assert rel_err(np.concatenate(got[i]), want[i]) < F32_TOL, f"request {i}"
+        check_close(np.concatenate(got[i]), want[i], dtype, f"request {i}")
     assert eng.stats().free_blocks == 13
     eng.close()
     model.close()
